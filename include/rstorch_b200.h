@@ -1,0 +1,252 @@
+/*
+ * rstorch_b200.h — C ABI of the B200 (sm_100a) training-step library.
+ *
+ * The library re-implements, on one or more B200 GPUs, the f64 training step of
+ * the `rstorch` crate: Sequential forward/backward through Linear and ReLU, the
+ * CrossEntropyLoss softmax-cross-entropy forward/backward, SGD::step and the
+ * batch assembly that feeds them.  The reference crate has no FFI of its own
+ * (it is pure Rust over ndarray), so each entry point below names the Rust
+ * function of the reference that a façade crate would route through it
+ * (paths are relative to the reference repository root).
+ *
+ * Conventions
+ *   - every tensor is a dense row-major matrix of f64 (the reference's
+ *     `Array2<f64>`, src/module/mod.rs:42-49), addressed by an opaque handle;
+ *   - every call returns an `rst_status`; 0 is success.  The reference panics
+ *     where this library returns an error (missing cache `unwrap()`,
+ *     src/module/linear.rs:61; shape mismatch inside `dot`); a façade maps a
+ *     non-zero status back to `panic!`;
+ *   - compute entry points are asynchronous on the context's compute stream;
+ *     the calls that hand a value to the host (`rst_tensor_download`,
+ *     `rst_xent_result`, `rst_accuracy`, `rst_argmax`, `rst_timer_elapsed_ms`)
+ *     block until it is ready;
+ *   - one context per GPU, used from one host thread at a time;
+ *   - there is no CPU fall-back anywhere: without a CUDA device every compute
+ *     entry point fails with RST_ERR_CUDA.
+ */
+#ifndef RSTORCH_B200_H
+#define RSTORCH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rst_ctx rst_ctx;         /* one GPU: streams, allocator, result ring   */
+typedef struct rst_tensor rst_tensor;   /* device matrix (rows, cols), f64, row-major */
+typedef struct rst_sgd_plan rst_sgd_plan; /* pointer table of one parameter set        */
+typedef struct rst_stager rst_stager;   /* pinned-host batch ring + copy stream       */
+typedef struct rst_comm rst_comm;       /* NCCL communicator bound to a context       */
+typedef struct rst_graph rst_graph;     /* captured CUDA graph of a step              */
+typedef struct rst_timer rst_timer;     /* pair of CUDA events on the compute stream  */
+
+typedef enum rst_status {
+    RST_OK = 0,
+    RST_ERR_INVALID_ARG = 1,    /* null pointer, negative size, bad flag             */
+    RST_ERR_SHAPE = 2,          /* operand shapes do not agree (ndarray would panic) */
+    RST_ERR_FOREIGN_HANDLE = 3, /* handle belongs to another context or is stale     */
+    RST_ERR_OOM = 4,            /* device allocation failed or the set limit is hit  */
+    RST_ERR_CUDA = 5,           /* a CUDA runtime/driver call failed                 */
+    RST_ERR_NCCL = 6,           /* NCCL missing or a collective failed               */
+    RST_ERR_DEVICE_TIMEOUT = 7, /* a bounded device-side wait gave up                */
+    RST_ERR_NAN = 8,            /* NaN logit: the reference panics in softmax `max`  */
+    RST_ERR_UNSUPPORTED = 9,    /* size beyond a documented maximum                  */
+    RST_ERR_STATE = 10          /* call out of order (e.g. result slot never written)*/
+} rst_status;
+
+/* ---- library ------------------------------------------------------------ */
+int rst_version(void);                       /* (major<<16)|(minor<<8)|patch */
+const char* rst_status_string(int status);
+/* Message of the last failing call made through `ctx` (or through a handle it
+ * owns).  With ctx == NULL: the last failure of a call that had no context. */
+const char* rst_last_error(const rst_ctx* ctx);
+
+/* ---- context ------------------------------------------------------------ */
+/* Creates the per-GPU state every other call needs: compute, copy and
+ * communication streams, the caching allocator that stands in for the
+ * reference's implicit `Array2` allocations (src/module/linear.rs:44,63,66,68;
+ * src/module/activation/relu.rs:20; src/optim/sgd.rs:23), and a ring of pinned
+ * result slots for the loss/accuracy read-back. */
+int rst_ctx_create(int device, rst_ctx** out);
+int rst_ctx_destroy(rst_ctx* ctx);
+int rst_ctx_synchronize(rst_ctx* ctx);
+int rst_ctx_device(const rst_ctx* ctx, int* device);
+/* Raw `cudaStream_t` of the compute stream (for callers that time or order
+ * their own work against it). */
+int rst_ctx_stream(const rst_ctx* ctx, void** stream);
+/* Reads and clears the device-side status word written by kernels whose
+ * bounded waits ran out; returns RST_ERR_DEVICE_TIMEOUT if it was set. */
+int rst_ctx_check_device(rst_ctx* ctx);
+/* Number of kernels this library has launched through `ctx` so far. */
+int rst_ctx_launch_count(const rst_ctx* ctx, uint64_t* count);
+
+/* Caching allocator controls.  stats[0..5] = bytes in use, bytes reserved from
+ * the driver, peak bytes in use, allocation requests, requests served from the
+ * cache, driver allocations. */
+int rst_ctx_memory_stats(const rst_ctx* ctx, uint64_t stats[6]);
+int rst_ctx_set_memory_limit(rst_ctx* ctx, uint64_t max_reserved_bytes); /* 0 = none */
+int rst_ctx_empty_cache(rst_ctx* ctx);
+
+/* ---- tensors -------------------------------------------------------------
+ * Stand-ins for `Array2<f64>` values that live in HBM.  A façade converts with
+ * upload/download at the edges of the step (`Array2::as_standard_layout` on
+ * the way in). */
+int rst_tensor_alloc(rst_ctx* ctx, int64_t rows, int64_t cols, rst_tensor** out);
+/* Non-owning window of `numel = rows*cols` elements starting `elem_offset`
+ * elements into `parent` (used to carve parameters and gradients out of one
+ * arena so that SGD and the gradient all-reduce see contiguous memory). */
+int rst_tensor_slice(rst_tensor* parent, int64_t elem_offset, int64_t rows, int64_t cols,
+                     rst_tensor** out);
+int rst_tensor_free(rst_tensor* t);
+int rst_tensor_shape(const rst_tensor* t, int64_t* rows, int64_t* cols);
+int rst_tensor_data(const rst_tensor* t, void** device_ptr);
+int rst_tensor_upload(rst_tensor* t, const double* host);     /* blocking */
+int rst_tensor_download(const rst_tensor* t, double* host);   /* blocking */
+int rst_tensor_copy(rst_tensor* dst, const rst_tensor* src);  /* device to device */
+int rst_tensor_fill(rst_tensor* t, double value);
+
+/* ---- Linear (src/module/linear.rs:41-79) ---------------------------------
+ * forward:  Y[B,out] = X[B,in] · W[out,in]ᵀ + b[1,out]   (linear.rs:44-53);
+ *           with relu != 0 the following ReLU::forward (relu.rs:21) is applied
+ *           in the same kernel: Y = max(Y, 0).  b may be NULL (bias-less).
+ * backward: n = rows(X);  dW[out,in] = dYᵀ·X / n  (linear.rs:62-63);
+ *           db[1,out] = Σ_rows dY / n              (linear.rs:65-67);
+ *           dX[B,in]  = dY · W, unscaled            (linear.rs:68).
+ *           If relu_mask_src is given (shape of dX) the ReLU::backward of the
+ *           layer in front (relu.rs:26) is fused in: dX *= (relu_mask_src > 0).
+ *           The post-ReLU output of that layer (= this layer's cached X) is a
+ *           valid mask source because max(x,0) > 0 ⇔ x > 0.
+ *           db and dX may be NULL to skip them (dX of the first layer is
+ *           discarded by the reference's training loop, README.md:72).
+ */
+int rst_linear_forward(rst_ctx* ctx, const rst_tensor* X, const rst_tensor* W,
+                       const rst_tensor* b, int relu, rst_tensor* Y);
+int rst_linear_backward(rst_ctx* ctx, const rst_tensor* dY, const rst_tensor* X,
+                        const rst_tensor* W, const rst_tensor* relu_mask_src,
+                        rst_tensor* dW, rst_tensor* db, rst_tensor* dX);
+
+/* ---- ReLU, unfused (src/module/activation/relu.rs:17-32) ----------------- */
+int rst_relu_forward(rst_ctx* ctx, const rst_tensor* X, rst_tensor* Y);
+/* dX = dY * (X_pre > 0 ? 1 : 0); X_pre is the tensor ReLU::forward cached. */
+int rst_relu_backward(rst_ctx* ctx, const rst_tensor* dY, const rst_tensor* X_pre,
+                      rst_tensor* dX);
+
+/* ---- softmax free function (src/module/activation/softmax.rs:36-53) ------ */
+int rst_softmax(rst_ctx* ctx, const rst_tensor* X, rst_tensor* P);
+
+/* ---- CrossEntropyLoss (src/loss/cross_entropy.rs:32-48) + accuracy --------
+ * One pass over the rows computes
+ *   p = softmax(logits, axis 1)                      (cross_entropy.rs:37)
+ *   loss = -(Σ_ij truth_ij · ln p_ij) / B            (cross_entropy.rs:38)
+ *   dlogits = p - truth, no 1/B                      (cross_entropy.rs:45-47)
+ *   correct = #{rows: argmax(logits) == argmax(truth)}, first maximum wins
+ *                                                    (src/utils.rs:44-65)
+ * and queues the three scalars into pinned result slot `slot`
+ * (0 <= slot < rst_xent_slots()).  dlogits may be NULL (loss only).
+ * rst_xent_result blocks until the slot is written and returns the loss and
+ * the accuracy (= correct / B).  It returns RST_ERR_NAN if a logit was NaN,
+ * the case in which the reference's softmax panics (softmax.rs:38). */
+int rst_xent_slots(void);
+int rst_xent_forward_backward(rst_ctx* ctx, const rst_tensor* logits, const rst_tensor* truth,
+                              rst_tensor* dlogits, int slot);
+int rst_xent_result(rst_ctx* ctx, int slot, double* loss, double* accuracy);
+
+/* Stand-alone `accuracy(pred, truth)` and row-wise `argmax` (src/utils.rs:44-65);
+ * blocking.  `idx` receives `rows` indices. */
+int rst_accuracy(rst_ctx* ctx, const rst_tensor* pred, const rst_tensor* truth, double* acc);
+int rst_argmax(rst_ctx* ctx, const rst_tensor* t, int64_t* idx);
+
+/* ---- SGD::step (src/optim/sgd.rs:18-25) -----------------------------------
+ * For every (param, grad) pair: param = param - (lr · grad), product rounded
+ * then difference rounded exactly as the reference's two ndarray operations do.
+ * A plan holds the device-side table of one parameter set so that a step is a
+ * single kernel launch whatever the number of tensors. */
+int rst_sgd_plan_create(rst_ctx* ctx, int n, rst_tensor* const* params,
+                        rst_tensor* const* grads, rst_sgd_plan** out);
+int rst_sgd_plan_step(rst_sgd_plan* plan, double lr);
+int rst_sgd_plan_destroy(rst_sgd_plan* plan);
+/* Convenience: builds (and caches on the context) the plan for this exact list. */
+int rst_sgd_step(rst_ctx* ctx, int n, rst_tensor* const* params, rst_tensor* const* grads,
+                 double lr);
+
+/* ---- batch staging (src/data/data_loader.rs:180-208) ----------------------
+ * `ArrayDataLoaderIter::next` appends `batch` samples into two fresh arrays.
+ * Here the loader writes the samples straight into a pinned host slot
+ * (rst_stager_host), rst_stager_submit starts the host→device copies on the
+ * copy stream, and rst_stager_acquire makes the compute stream wait for them
+ * and hands out the device tensors of that slot.  A slot may be rewritten once
+ * work that reads its device tensors has been queued and a later submit of
+ * the same slot is ordered after it (the library inserts that dependency). */
+int rst_stager_create(rst_ctx* ctx, int64_t batch, int64_t x_cols, int64_t t_cols, int slots,
+                      rst_stager** out);
+int rst_stager_destroy(rst_stager* s);
+int rst_stager_host(rst_stager* s, int slot, double** x_host, double** t_host);
+int rst_stager_submit(rst_stager* s, int slot);
+int rst_stager_acquire(rst_stager* s, int slot, rst_tensor** X, rst_tensor** T);
+
+/* ---- data-parallel gradient exchange (no counterpart in the reference, which
+ * is single-threaded; required to shard the batch over the GPUs of one box) --
+ * One rank per process/GPU.  Rank 0 obtains an id, the caller ships the
+ * RST_COMM_ID_BYTES bytes to the other ranks by any means, every rank calls
+ * rst_comm_create.  rst_allreduce_avg averages each tensor over the ranks
+ * (with equal shards, the average of the per-rank dW = dYᵀX/(B/G) is the
+ * full-batch dW = dYᵀX/B of linear.rs:63).  It runs on the communication
+ * stream, ordered after the compute work queued so far; rst_comm_join makes
+ * the compute stream wait for all exchanges queued so far. */
+#define RST_COMM_ID_BYTES 128
+int rst_comm_get_id(void* id_bytes);
+int rst_comm_create(rst_ctx* ctx, const void* id_bytes, int rank, int world, rst_comm** out);
+int rst_comm_destroy(rst_comm* comm);
+int rst_allreduce_avg(rst_comm* comm, int n, rst_tensor* const* tensors);
+int rst_comm_join(rst_comm* comm);
+
+/* ---- whole-step replay ------------------------------------------------------
+ * Captures everything queued on the compute stream between begin and end into
+ * a CUDA graph (configs whose step is a dozen short kernels are launch-bound).
+ * Calls that block or allocate from the driver are not allowed in between. */
+int rst_graph_capture_begin(rst_ctx* ctx);
+int rst_graph_capture_end(rst_ctx* ctx, rst_graph** out);
+int rst_graph_launch(rst_graph* g);
+int rst_graph_destroy(rst_graph* g);
+
+/* ---- synthetic input streams (host only; no counterpart in the reference,
+ * whose initialiser draws from an unseedable thread generator,
+ * src/module/init/he.rs:13) -------------------------------------------------
+ * Word i of stream `key` is splitmix64(key + i·φ64); any slice of a stream can
+ * be produced independently.  rst_synth_uniform writes n values of U[0,1)
+ * starting at element `offset`; rst_synth_normal writes N(mean, stddev) by
+ * Box-Muller (element i uses words 2i and 2i+1). */
+int rst_synth_uniform(uint64_t key, uint64_t n, uint64_t offset, double* out);
+int rst_synth_normal(uint64_t key, uint64_t n, uint64_t offset, double mean, double stddev,
+                     double* out);
+
+/* ---- timing and roofline probes ------------------------------------------- */
+int rst_timer_create(rst_ctx* ctx, rst_timer** out);
+int rst_timer_start(rst_timer* t);   /* records on the compute stream */
+int rst_timer_stop(rst_timer* t);
+int rst_timer_elapsed_ms(rst_timer* t, double* ms);  /* blocking */
+int rst_timer_destroy(rst_timer* t);
+/* Per-kernel-class device time.  Between begin and end every launch group of
+ * the library (gemm_fwd, gemm_dW, gemm_dX, colsum, xent, sgd, relu_fwd, relu_bwd)
+ * is bracketed by CUDA events on the compute stream; end blocks and writes
+ * lines "name launches milliseconds" into `report`.  The extra events perturb
+ * short kernels, so timed benchmark regions run with profiling off. */
+int rst_profile_begin(rst_ctx* ctx);
+int rst_profile_end(rst_ctx* ctx, char* report, size_t capacity);
+/* Register-resident issue-rate probe of the f64 tensor instruction the GEMM
+ * kernels use (kind 0: mma.sync m16n8k8 f64, 1: m8n8k4, 2: m16n8k16,
+ * 3: plain DFMA); returns TFLOP/s over the whole GPU.  This is the measured
+ * denominator of the GEMM roofline. */
+int rst_probe_fp64_peak(rst_ctx* ctx, int kind, int iters, double* tflops);
+/* Device-to-device streaming copy of `bytes` (read + write counted), GB/s. */
+int rst_probe_hbm_copy(rst_ctx* ctx, uint64_t bytes, int iters, double* gbs);
+/* Writes `bytes` of a scratch buffer (pass > L2 size to flush L2 between timed
+ * iterations). */
+int rst_flush_l2(rst_ctx* ctx, uint64_t bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RSTORCH_B200_H */

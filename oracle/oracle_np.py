@@ -1,0 +1,103 @@
+"""TEST INFRASTRUCTURE: numpy twin of the CPU restatement (small cases only).
+
+Each function restates one reference function with numpy array expressions that
+mirror the ndarray expressions of the Rust source line by line; it cross-checks
+the C++ restatement and generates the committed golden fixtures.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+F64_MIN = -np.finfo(np.float64).max
+
+
+def linear_forward(X, W, b=None):
+    """src/module/linear.rs:43-57: input.dot(&weight.t()) then x += bias."""
+    y = X @ W.T
+    if b is not None:
+        y = y + b.reshape(1, -1)
+    return y
+
+
+def linear_backward(dY, X, W):
+    """src/module/linear.rs:60-69: (gradient.t().dot(prev_input)/n, sum_axis(0)/n as (1,out), gradient.dot(weight))."""
+    n = float(X.shape[0])
+    dW = (dY.T @ X) / n
+    db = (dY.sum(axis=0) / n)[None, :]
+    dX = dY @ W
+    return dW, db, dX
+
+
+def relu_forward(x):
+    """src/module/activation/relu.rs:21: x.max(0.0) with f64::max (NaN -> 0)."""
+    return np.where(np.isnan(x), 0.0, np.maximum(x, 0.0))
+
+
+def relu_backward(dy, xpre):
+    """src/module/activation/relu.rs:26: gradient * f64::from(x > 0.0)."""
+    return dy * (xpre > 0.0).astype(np.float64)
+
+
+def softmax(x):
+    """src/module/activation/softmax.rs:45-53 (axis 1)."""
+    m = np.maximum(np.max(np.where(np.isnan(x), F64_MIN, x), axis=1, keepdims=True), F64_MIN)
+    e = np.exp(x - m)
+    return e / e.sum(axis=1, keepdims=True)
+
+
+def xent_forward(pred, truth):
+    """src/loss/cross_entropy.rs:34-42 -> (loss, cached softmax)."""
+    p = softmax(pred)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        loss = -(truth * np.log(p)).sum() / float(pred.shape[0])
+    return float(loss), p
+
+
+def xent_backward(p, truth):
+    """src/loss/cross_entropy.rs:45-47."""
+    return -(truth - p)
+
+
+def sgd_step(p, g, lr):
+    """src/optim/sgd.rs:23: parm - (lr * grad); numpy rounds the product, then the difference."""
+    return p - (lr * g)
+
+
+def argmax(x):
+    """src/utils.rs:44-53: first maximum wins, replace only on strict `>`."""
+    out = np.zeros(x.shape[0], dtype=np.int64)
+    for r in range(x.shape[0]):
+        best, bv = 0, x[r, 0]
+        for c in range(1, x.shape[1]):
+            if x[r, c] > bv:
+                best, bv = c, x[r, c]
+        out[r] = best
+    return out
+
+
+def accuracy(pred, truth):
+    """src/utils.rs:55-65."""
+    return float((argmax(pred) == argmax(truth)).sum()) / float(pred.shape[0])
+
+
+def mlp_step(weights, X, T, lr, skip_first_dx=False):
+    """One step in the order of src/model.rs:19-27 for Linear,ReLU,...,Linear.
+    Returns (loss, acc, grads, new_weights, logits)."""
+    acts, pres = [X], []
+    for l, (W, b) in enumerate(weights):
+        z = linear_forward(acts[-1], W, b)
+        pres.append(z)
+        acts.append(relu_forward(z) if l + 1 < len(weights) else z)
+    logits = pres[-1]
+    loss, p = xent_forward(logits, T)
+    acc = accuracy(logits, T)
+    g = xent_backward(p, T)
+    grads = [None] * len(weights)
+    for l in range(len(weights) - 1, -1, -1):
+        W, _ = weights[l]
+        dW, db, dX = linear_backward(g, acts[l], W)
+        grads[l] = (dW, db)
+        if l > 0:
+            g = relu_backward(dX, pres[l - 1])
+    new = [(sgd_step(W, dW, lr), sgd_step(b, db, lr)) for (W, b), (dW, db) in zip(weights, grads)]
+    return loss, acc, grads, new, logits

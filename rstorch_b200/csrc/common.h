@@ -1,0 +1,168 @@
+// Internal declarations shared by the translation units of librstorch_b200.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/rstorch_b200.h"
+
+namespace rst {
+
+constexpr uint32_t kCtxMagic = 0x52535443u;     // 'RSTC'
+constexpr uint32_t kTensorMagic = 0x52535454u;  // 'RSTT'
+constexpr uint32_t kDeadMagic = 0xDEADBEEFu;
+constexpr int kXentSlots = 64;
+constexpr int kNumSMsFallback = 148;
+
+// Device status word indices (written by kernels, read by rst_ctx_check_device).
+enum DeviceStatus : int { kDevOk = 0, kDevBarrierTimeout = 1 };
+
+// ---------------------------------------------------------------------------
+// Caching allocator: size-bucketed free lists over cudaMalloc.  All tensors of
+// a context are used in the order of its compute stream, so a block handed back
+// by rst_tensor_free can be reused by the next request without an event.
+// ---------------------------------------------------------------------------
+class CachingAllocator {
+public:
+    // Rounds a request to its bucket size: 512 B granules below 1 MiB (in
+    // quarter-octave steps above 4 KiB), 2 MiB granules above.
+    static size_t bucket_size(size_t bytes);
+
+    // Returns nullptr and sets *err on failure (cudaError value or -1 = limit).
+    void* allocate(size_t bytes, size_t* granted, int* err, bool may_call_driver);
+    void release(void* ptr, size_t granted);
+    void empty_cache();
+    void set_limit(uint64_t max_reserved) { limit_ = max_reserved; }
+
+    uint64_t in_use = 0, reserved = 0, peak = 0, requests = 0, hits = 0, driver_allocs = 0;
+
+private:
+    std::multimap<size_t, void*> free_;
+    uint64_t limit_ = 0;
+};
+
+struct ResultSlot {  // written by the xent kernel, copied to pinned host memory
+    double loss_sum;    // Σ_ij t_ij · ln p_ij  (sign and 1/B applied on the host)
+    double correct;     // rows whose argmax(logits) == argmax(truth)
+    double rows;        // B
+    double nan_rows;    // rows holding a NaN logit
+};
+
+}  // namespace rst
+
+struct rst_tensor {
+    uint32_t magic;
+    rst_ctx* ctx;
+    double* data;
+    int64_t rows, cols;
+    size_t granted;      // bytes obtained from the allocator (0 for views)
+    bool owns;
+};
+
+struct rst_ctx {
+    uint32_t magic;
+    int device;
+    int num_sms;
+    cudaStream_t compute, copy, comm;
+    rst::CachingAllocator alloc;
+    std::string last_error;
+    uint64_t launches;
+    bool capturing;
+
+    int* d_status;            // device status words (kernels report bounded-wait expiry)
+    int* h_status;            // pinned mirror
+
+    // loss / accuracy read-back ring
+    rst::ResultSlot* d_results;
+    rst::ResultSlot* h_results;   // pinned
+    cudaEvent_t result_event[rst::kXentSlots];
+    bool result_pending[rst::kXentSlots];
+    bool result_in_graph[rst::kXentSlots];   // written by a captured graph: no event to wait on
+
+    // scratch owned by the context and grown on demand
+    double* xent_partials;  size_t xent_partials_cap;   // per-block partial sums
+    unsigned int* xent_counter;                          // last-block election
+    double* splitk_ws;      size_t splitk_ws_bytes;     // split-K partial tiles
+    double* colsum_ws;      size_t colsum_ws_bytes;     // two-pass column sums
+    char* flush_buf;        size_t flush_bytes;
+
+    void* encode_tiled;     // PFN_cuTensorMapEncodeTiled, resolved at creation
+
+    // per-kernel-class timing (rst_profile_begin/end): event pairs around launches
+    bool profiling;
+    struct ProfRecord { const char* name; cudaEvent_t start, stop; };
+    std::vector<ProfRecord> prof_records;
+    std::vector<cudaEvent_t> prof_event_pool;
+    std::map<std::string, rst_sgd_plan*> plan_cache;
+};
+
+namespace rst {
+
+int fail(const rst_ctx* ctx, int status, const char* fmt, ...);
+bool valid(const rst_ctx* ctx);
+bool valid(const rst_tensor* t);
+int check_tensor(const rst_ctx* ctx, const rst_tensor* t, const char* name);
+// Grows a context-owned scratch buffer (never during graph capture).
+int ensure_scratch(rst_ctx* ctx, void** buf, size_t* cap, size_t need, const char* what);
+int after_launch(rst_ctx* ctx, const char* what);
+
+// Brackets the launches of one kernel class with CUDA events while profiling is on.
+class ProfScope {
+public:
+    ProfScope(rst_ctx* ctx, const char* name);
+    ~ProfScope();
+private:
+    rst_ctx* ctx_;
+    int index_;
+};
+
+#define RST_CUDA(ctx, call)                                                            \
+    do {                                                                               \
+        cudaError_t e__ = (call);                                                      \
+        if (e__ != cudaSuccess)                                                        \
+            return rst::fail((ctx), RST_ERR_CUDA, "%s failed: %s (%s:%d)", #call,      \
+                             cudaGetErrorString(e__), __FILE__, __LINE__);             \
+    } while (0)
+
+#define RST_TRY(call)                      \
+    do {                                   \
+        int s__ = (call);                  \
+        if (s__ != RST_OK) return s__;     \
+    } while (0)
+
+// ---- kernel launchers implemented in the .cu files -------------------------
+enum GemmEpilogue : int { kEpiNone = 0, kEpiBias = 1, kEpiBiasRelu = 2, kEpiDivN = 3, kEpiMask = 4 };
+
+struct GemmArgs {
+    // C[M,N] = op(A)·op(B); A is K-major ([M][K] in memory) or M-major ([K][M]);
+    // B is K-major ([N][K]) or N-major ([K][N]).
+    const double* A; const double* B; double* C;
+    int64_t M, N, K;
+    bool a_kmajor, b_kmajor;
+    int epilogue;
+    const double* bias;       // [N]          (kEpiBias, kEpiBiasRelu)
+    const double* mask_src;   // [M,N]        (kEpiMask)
+    double divisor;           // n            (kEpiDivN)
+};
+int launch_gemm(rst_ctx* ctx, const GemmArgs& a);
+
+int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols, double n,
+                      double* out);
+int launch_relu_forward(rst_ctx* ctx, const double* x, double* y, int64_t n);
+int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, double* dx,
+                         int64_t n);
+int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n);
+int launch_softmax(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols);
+int launch_xent(rst_ctx* ctx, const double* logits, const double* truth, double* dlogits,
+                int64_t rows, int64_t cols, ResultSlot* d_slot);
+int launch_argmax(rst_ctx* ctx, const double* x, int64_t rows, int64_t cols, long long* d_idx);
+
+}  // namespace rst

@@ -1,0 +1,165 @@
+// Unfused ReLU forward/backward, fill, and the two-pass column sum behind db.
+// All of them are HBM-streaming kernels: 16-byte vector accesses on the aligned
+// body, grids sized in multiples of the SM count.
+#include "common.h"
+
+namespace rst {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ double relu1(double v) { return fmax(v, 0.0); }  // NaN -> 0 like f64::max
+__device__ __forceinline__ double gate1(double dy, double x) { return dy * (x > 0.0 ? 1.0 : 0.0); }
+
+// y = max(x, 0)                                   (src/module/activation/relu.rs:21)
+__global__ void __launch_bounds__(kThreads) relu_forward_kernel(const double* __restrict__ x,
+                                                                double* __restrict__ y, int64_t n,
+                                                                int vec_ok) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    if (vec_ok) {
+        int64_t n2 = n >> 1;
+        const double2* x2 = reinterpret_cast<const double2*>(x);
+        double2* y2 = reinterpret_cast<double2*>(y);
+        for (int64_t i = tid; i < n2; i += stride) {
+            double2 v = x2[i];
+            v.x = relu1(v.x); v.y = relu1(v.y);
+            y2[i] = v;
+        }
+        if (tid == 0 && (n & 1)) y[n - 1] = relu1(x[n - 1]);
+    } else {
+        for (int64_t i = tid; i < n; i += stride) y[i] = relu1(x[i]);
+    }
+}
+
+// dx = dy * (x_pre > 0 ? 1 : 0)                   (src/module/activation/relu.rs:26)
+__global__ void __launch_bounds__(kThreads) relu_backward_kernel(const double* __restrict__ dy,
+                                                                 const double* __restrict__ xpre,
+                                                                 double* __restrict__ dx, int64_t n,
+                                                                 int vec_ok) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    if (vec_ok) {
+        int64_t n2 = n >> 1;
+        const double2* g2 = reinterpret_cast<const double2*>(dy);
+        const double2* x2 = reinterpret_cast<const double2*>(xpre);
+        double2* o2 = reinterpret_cast<double2*>(dx);
+        for (int64_t i = tid; i < n2; i += stride) {
+            double2 g = g2[i], v = x2[i];
+            g.x = gate1(g.x, v.x); g.y = gate1(g.y, v.y);
+            o2[i] = g;
+        }
+        if (tid == 0 && (n & 1)) dx[n - 1] = gate1(dy[n - 1], xpre[n - 1]);
+    } else {
+        for (int64_t i = tid; i < n; i += stride) dx[i] = gate1(dy[i], xpre[i]);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) fill_kernel(double* __restrict__ x, double v, int64_t n) {
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n; i += stride) x[i] = v;
+}
+
+// Column sums of dY[rows, cols] in two deterministic passes.
+// Pass 1: block (bx, by) sums rows [by*rows_per, ...) of columns [bx*128, +128) into
+// ws[by][col].  Pass 2: sums the `parts` partial rows in index order and divides by n.
+constexpr int kColsPerBlock = 128;
+constexpr int kRowLanes = 2;   // 256 threads = 128 columns x 2 row lanes
+
+__global__ void __launch_bounds__(kThreads) colsum_pass1(const double* __restrict__ dY, int64_t rows,
+                                                         int64_t cols, int64_t rows_per,
+                                                         double* __restrict__ ws) {
+    __shared__ double sh[kRowLanes][kColsPerBlock];
+    int c_local = threadIdx.x % kColsPerBlock;
+    int lane_r = threadIdx.x / kColsPerBlock;
+    int64_t col = (int64_t)blockIdx.x * kColsPerBlock + c_local;
+    int64_t r0 = (int64_t)blockIdx.y * rows_per;
+    int64_t r1 = r0 + rows_per < rows ? r0 + rows_per : rows;
+    double acc = 0.0;
+    if (col < cols) {
+        // four independent partial sums keep several loads in flight per thread
+        double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+        int64_t r = r0 + lane_r;
+        for (; r + 3 * kRowLanes < r1; r += 4 * kRowLanes) {
+            a0 += dY[r * cols + col];
+            a1 += dY[(r + kRowLanes) * cols + col];
+            a2 += dY[(r + 2 * kRowLanes) * cols + col];
+            a3 += dY[(r + 3 * kRowLanes) * cols + col];
+        }
+        for (; r < r1; r += kRowLanes) a0 += dY[r * cols + col];
+        acc = (a0 + a1) + (a2 + a3);
+    }
+    sh[lane_r][c_local] = acc;
+    __syncthreads();
+    if (lane_r == 0 && col < cols) ws[(int64_t)blockIdx.y * cols + col] = sh[0][c_local] + sh[1][c_local];
+}
+
+// db = (Σ_rows dY) / n                              (src/module/linear.rs:65-67)
+__global__ void __launch_bounds__(kThreads) colsum_pass2(const double* __restrict__ ws, int parts,
+                                                         int64_t cols, double n,
+                                                         double* __restrict__ out) {
+    int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= cols) return;
+    double acc = 0.0;
+    for (int p = 0; p < parts; ++p) acc += ws[(int64_t)p * cols + col];
+    out[col] = acc / n;
+}
+
+inline int grid_for(const rst_ctx* ctx, int64_t work_items, int per_sm) {
+    int64_t blocks = (work_items + kThreads - 1) / kThreads;
+    int64_t cap = (int64_t)ctx->num_sms * per_sm;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+}  // namespace
+
+int launch_relu_forward(rst_ctx* ctx, const double* x, double* y, int64_t n) {
+    if (n == 0) return RST_OK;
+    int vec = aligned16(x) && aligned16(y);
+    relu_forward_kernel<<<grid_for(ctx, vec ? n / 2 + 1 : n, 8), kThreads, 0, ctx->compute>>>(x, y, n, vec);
+    return after_launch(ctx, "relu_forward_kernel");
+}
+
+int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, double* dx, int64_t n) {
+    if (n == 0) return RST_OK;
+    int vec = aligned16(dy) && aligned16(xpre) && aligned16(dx);
+    relu_backward_kernel<<<grid_for(ctx, vec ? n / 2 + 1 : n, 8), kThreads, 0, ctx->compute>>>(dy, xpre, dx, n, vec);
+    return after_launch(ctx, "relu_backward_kernel");
+}
+
+int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n) {
+    if (n == 0) return RST_OK;
+    fill_kernel<<<grid_for(ctx, n, 8), kThreads, 0, ctx->compute>>>(x, v, n);
+    return after_launch(ctx, "fill_kernel");
+}
+
+int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols, double n,
+                      double* out) {
+    if (cols == 0) return RST_OK;
+    int64_t col_blocks = (cols + kColsPerBlock - 1) / kColsPerBlock;
+    // enough row parts to fill the GPU about four times over, at least 64 rows each
+    int64_t want_parts = ((int64_t)ctx->num_sms * 4 + col_blocks - 1) / col_blocks;
+    int64_t max_parts = (rows + 63) / 64;
+    int64_t parts = want_parts < max_parts ? want_parts : max_parts;
+    if (parts < 1) parts = 1;
+    if (parts > 65535) parts = 65535;
+    int64_t rows_per = (rows + parts - 1) / parts;
+    if (rows_per < 1) rows_per = 1;
+    parts = rows == 0 ? 1 : (rows + rows_per - 1) / rows_per;
+    size_t need = (size_t)parts * (size_t)cols * sizeof(double);
+    RST_TRY(ensure_scratch(ctx, (void**)&ctx->colsum_ws, &ctx->colsum_ws_bytes, need, "column-sum"));
+    dim3 g1((unsigned)col_blocks, (unsigned)parts);
+    colsum_pass1<<<g1, kThreads, 0, ctx->compute>>>(dY, rows, cols, rows_per, ctx->colsum_ws);
+    RST_TRY(after_launch(ctx, "colsum_pass1"));
+    int g2 = (int)((cols + kThreads - 1) / kThreads);
+    colsum_pass2<<<g2, kThreads, 0, ctx->compute>>>(ctx->colsum_ws, (int)parts, cols, n, out);
+    return after_launch(ctx, "colsum_pass2");
+}
+
+}  // namespace rst

@@ -1,0 +1,382 @@
+// f64 GEMM for Linear forward/backward on sm_100a: TMA-staged shared-memory tiles,
+// an mbarrier ring between one producer warp and the consumer warps, DMMA
+// (mma.sync m16n8k8 f64) from registers, and the bias / ReLU / 1/n / ReLU-mask
+// epilogues applied to the accumulators before the single store of C.
+//
+//   forward   Y  = X · Wᵀ + b      A = X  [M][K] (K-major)   B = W [N][K] (K-major)
+//   backward  dX = dY · W          A = dY [M][K] (K-major)   B = W [K][N] (N-major)
+//   backward  dW = dYᵀ · X / n     A = dY [K][M] (M-major)   B = X [K][N] (N-major)
+// (src/module/linear.rs:44, :68, :63 of the reference.)
+//
+// Shared-memory tiles are rows of 16 f64 = 128 bytes written by TMA with the
+// 128-byte swizzle (16-byte chunk index XOR row%8), so every fragment is read
+// with 16-byte shared loads.  The mma k index and, for M-/N-major operands, the
+// m/n index of a fragment element are free to permute as long as A and B agree
+// on k and the epilogue knows where each accumulator lives; the mappings below
+// pick the permutation that makes one 16-byte load deliver two fragment elements.
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+
+#include "common.h"
+#include "mma_f64.cuh"
+
+namespace rst {
+namespace {
+
+constexpr int kBK = 16;            // k extent of a stage: one 128-byte row of f64
+constexpr int kRowBytes = 128;
+constexpr int kBoxBytes = 16 * kRowBytes;   // 16x16 box of an M-/N-major operand
+
+struct GemmParams {
+    double* C;
+    const double* bias;
+    const double* mask_src;
+    double* splitk_ws;      // [splits][M][N] raw partial sums when splits > 1
+    int* status;
+    double divisor;
+    long long M, N, K;
+    int tiles_m, tiles_n;
+    int k_tiles;            // ceil(K / 16)
+    int k_tiles_per_split;
+    int splits;
+    int epilogue;
+};
+
+__device__ __forceinline__ double apply_epilogue(const GemmParams& p, double v, long long r, long long c) {
+    switch (p.epilogue) {
+        case kEpiBias: return v + p.bias[c];
+        case kEpiBiasRelu: return fmax(v + p.bias[c], 0.0);
+        case kEpiDivN: return v / p.divisor;
+        case kEpiMask: return v * (p.mask_src[r * p.N + c] > 0.0 ? 1.0 : 0.0);
+        default: return v;
+    }
+}
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
+struct Cfg {
+    static_assert(A_K || !B_K, "M-major A with K-major B is not used by Linear");
+    static constexpr int kConsumerWarps = WARPS_M * WARPS_N;
+    static constexpr int kThreads = (kConsumerWarps + 1) * 32;
+    static constexpr int WTM = BM / WARPS_M, WTN = BN / WARPS_N;
+    static constexpr int MT = WTM / 16, NT = WTN / 8;
+    static_assert(WTM % 16 == 0 && WTN % 16 == 0, "warp tile must be a multiple of 16x16");
+    static constexpr int kABytes = BM * kRowBytes;
+    static constexpr int kBBytes = BN * kRowBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kSmemBytes = STAGES * kStageBytes + 1024 /*alignment slack*/ + 2 * STAGES * 8;
+    // k permutation: both operands M-/N-major -> pairs (2t, 2t+1); otherwise the
+    // K-major operand dictates pairs (4t+2i, 4t+2i+1).
+    static constexpr bool kMnNatural = !A_K && !B_K;
+};
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
+__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const GemmParams p) {
+    using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
+    constexpr int MT = C_::MT, NT = C_::NT;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + STAGES * C_::kStageBytes;   // full[STAGES], empty[STAGES]
+    auto full_bar = [&](int s) { return bars + (uint32_t)s * 8u; };
+    auto empty_bar = [&](int s) { return bars + (uint32_t)(STAGES + s) * 8u; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // tile coordinates: groups of 8 tile rows share their B tiles in L2
+    constexpr int kGroup = 8;
+    const int tiles_per_group = kGroup * p.tiles_n;
+    const int group = blockIdx.x / tiles_per_group;
+    const int first_m = group * kGroup;
+    const int group_rows = min(p.tiles_m - first_m, kGroup);
+    const int in_group = blockIdx.x - group * tiles_per_group;
+    const int tile_m = first_m + in_group % group_rows;
+    const int tile_n = in_group / group_rows;
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
+    const int split = blockIdx.y;
+    const int kt_begin = split * p.k_tiles_per_split;
+    const int kt_end = min(kt_begin + p.k_tiles_per_split, p.k_tiles);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), C_::kConsumerWarps);
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    if (warp == C_::kConsumerWarps) {
+        // ---------------- producer warp: one lane drives TMA ----------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA);
+            tma_prefetch_desc(&tmB);
+            int it = 0;
+            for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u)) {
+                    atomicExch(p.status, kDevBarrierTimeout);
+                    atomicExch(p.status + 1, 1);
+                    break;
+                }
+                mbar_expect_tx(full_bar(s), C_::kStageBytes);
+                const uint32_t As = smem_base + (uint32_t)s * C_::kStageBytes;
+                const uint32_t Bs = As + C_::kABytes;
+                const int k0 = kt * kBK;
+                if (A_K) {
+                    tma_load_2d(As, &tmA, k0, m0, full_bar(s));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BM / 16; ++j)
+                        tma_load_2d(As + j * kBoxBytes, &tmA, m0 + j * 16, k0, full_bar(s));
+                }
+                if (B_K) {
+                    tma_load_2d(Bs, &tmB, k0, n0, full_bar(s));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < BN / 16; ++j)
+                        tma_load_2d(Bs + j * kBoxBytes, &tmB, n0 + j * 16, k0, full_bar(s));
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    const int wm = warp / WARPS_N, wn = warp % WARPS_N;
+    const int g = lane >> 2, t = lane & 3;
+
+    double acc[MT][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.0;
+
+    // Per-thread byte offsets inside a stage that do not depend on the k sub-step.
+    // K-major operand: row*128, chunk (2t+i) ^ (row%8) with row%8 == g.
+    const uint32_t a_row_off = (uint32_t)(wm * C_::WTM + g) * kRowBytes;          // + mt*16*128 (+8 rows: +1024)
+    const uint32_t b_row_off = (uint32_t)(wn * C_::WTN + g) * kRowBytes;          // + nt*8*128
+    const uint32_t kchunk0 = (uint32_t)((2 * t) ^ g) << 4;                        // i = 0; i = 1 flips bit 4
+    // M-/N-major operand: box base + k*128 + ((g ^ k%8) << 4)
+    const uint32_t a_box_off = (uint32_t)(wm * C_::WTM / 16) * kBoxBytes;         // + mt*2048
+    const uint32_t b_box_off = (uint32_t)(wn * C_::WTN / 16) * kBoxBytes;         // + (nt/2)*2048
+
+    bool ok = true;
+    int it = 0;
+    for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        if (!mbar_wait_bounded(full_bar(s), ph)) {
+            atomicExch(p.status, kDevBarrierTimeout);
+            atomicExch(p.status + 1, 2);
+            ok = false;
+            break;
+        }
+        const uint32_t As = smem_base + (uint32_t)s * C_::kStageBytes;
+        const uint32_t Bs = As + C_::kABytes;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            // rows of an M-/N-major tile that feed logical k = t and k = t+4 of this sub-step
+            const int kr0 = C_::kMnNatural ? (8 * i + 2 * t) : (4 * t + 2 * i);
+            const int kr1 = kr0 + 1;
+            const uint32_t mn_off0 = (uint32_t)kr0 * kRowBytes + ((uint32_t)(g ^ (kr0 & 7)) << 4);
+            const uint32_t mn_off1 = (uint32_t)kr1 * kRowBytes + ((uint32_t)(g ^ (kr1 & 7)) << 4);
+            const uint32_t kchunk = kchunk0 ^ ((uint32_t)i << 4);
+
+            double a[MT][4], b[NT][2];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                if (A_K) {
+                    const uint32_t addr = As + a_row_off + (uint32_t)mt * 16 * kRowBytes + kchunk;
+                    lds128(a[mt][0], a[mt][2], addr);                 // row g   : k = t, t+4
+                    lds128(a[mt][1], a[mt][3], addr + 8 * kRowBytes); // row g+8
+                } else {
+                    const uint32_t box = As + a_box_off + (uint32_t)mt * kBoxBytes;
+                    lds128(a[mt][0], a[mt][1], box + mn_off0);        // k = t   : m = 2g, 2g+1
+                    lds128(a[mt][2], a[mt][3], box + mn_off1);        // k = t+4
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                if (B_K) {
+                    const uint32_t addr = Bs + b_row_off + (uint32_t)nt * 8 * kRowBytes + kchunk;
+                    lds128(b[nt][0], b[nt][1], addr);                 // n = g : k = t, t+4
+                } else if ((nt & 1) == 0) {
+                    const uint32_t box = Bs + b_box_off + (uint32_t)(nt / 2) * kBoxBytes;
+                    lds128(b[nt][0], b[nt + 1][0], box + mn_off0);    // k = t   : n = 2g (even tile), 2g+1 (odd tile)
+                    lds128(b[nt][1], b[nt + 1][1], box + mn_off1);    // k = t+4
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) dmma_m16n8k8(acc[mt][nt], a[mt], b[nt]);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+    }
+    if (!ok) return;
+
+    // ---------------- epilogue: registers -> global ----------------
+    const bool raw = p.splits > 1;
+    double* out = raw ? p.splitk_ws + (long long)split * p.M * p.N : p.C;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            // logical row g (h = 0) or g+8 (h = 1) of this m-tile
+            const long long r = m0 + wm * C_::WTM + mt * 16 + (A_K ? (g + 8 * h) : (2 * g + h));
+            if (r >= p.M) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    long long c;
+                    if (B_K) c = n0 + wn * C_::WTN + nt * 8 + 2 * t + e;
+                    else c = n0 + wn * C_::WTN + (nt & ~1) * 8 + 4 * t + 2 * e + (nt & 1);
+                    if (c >= p.N) continue;
+                    double v = acc[mt][nt][2 * h + e];
+                    if (!raw) v = apply_epilogue(p, v, r, c);
+                    out[r * p.N + c] = v;
+                }
+            }
+        }
+    }
+}
+
+// Sums the split-K partials in split order and applies the epilogue.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
+    const long long total = p.M * p.N;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        double v = 0.0;
+        for (int z = 0; z < p.splits; ++z) v += p.splitk_ws[(long long)z * total + i];
+        p.C[i] = apply_epilogue(p, v, i / p.N, i % p.N);
+    }
+}
+
+// Plain-load kernel for operands TMA cannot address (odd row pitch or a base
+// that is not 16-byte aligned); shapes like the reference's own 3x2 unit tests.
+__global__ void __launch_bounds__(256)
+gemm_f64_plain(const double* __restrict__ A, const double* __restrict__ B, long long sam, long long sak,
+               long long sbk, long long sbn, const GemmParams p) {
+    const long long total = p.M * p.N;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long r = i / p.N, c = i % p.N;
+        double v = 0.0;
+        for (long long k = 0; k < p.K; ++k) v = fma(A[r * sam + k * sak], B[k * sbk + c * sbn], v);
+        p.C[i] = apply_epilogue(p, v, r, c);
+    }
+}
+
+int encode_map(rst_ctx* ctx, CUtensorMap* map, const double* base, long long inner, long long outer,
+               int box_inner, int box_outer) {
+    auto fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ctx->encode_tiled);
+    cuuint64_t gdim[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t gstride[1] = {(cuuint64_t)inner * sizeof(double)};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 2, const_cast<double*>(base), gdim, gstride, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, RST_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (inner %lld, outer %lld)",
+                    (int)r, inner, outer);
+    return RST_OK;
+}
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
+int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
+    using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
+    auto kernel = gemm_f64_tma_dmma<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
+    static bool attr_set[16] = {false};   // per device
+    if (!attr_set[ctx->device & 15]) {
+        RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes));
+        attr_set[ctx->device & 15] = true;
+    }
+    CUtensorMap tmA, tmB;
+    if (A_K) RST_TRY(encode_map(ctx, &tmA, a.A, a.K, a.M, kBK, BM));
+    else     RST_TRY(encode_map(ctx, &tmA, a.A, a.M, a.K, 16, kBK));
+    if (B_K) RST_TRY(encode_map(ctx, &tmB, a.B, a.K, a.N, kBK, BN));
+    else     RST_TRY(encode_map(ctx, &tmB, a.B, a.N, a.K, 16, kBK));
+
+    p.tiles_m = (int)((a.M + BM - 1) / BM);
+    p.tiles_n = (int)((a.N + BN - 1) / BN);
+    p.k_tiles = (int)((a.K + kBK - 1) / kBK);
+    p.splits = splits;
+    p.k_tiles_per_split = (p.k_tiles + splits - 1) / splits;
+    if (p.k_tiles_per_split < 1) p.k_tiles_per_split = 1;
+    p.splits = std::max(1, (p.k_tiles + p.k_tiles_per_split - 1) / p.k_tiles_per_split);
+    if (p.splits > 1) {
+        size_t need = (size_t)p.splits * (size_t)a.M * (size_t)a.N * sizeof(double);
+        RST_TRY(ensure_scratch(ctx, (void**)&ctx->splitk_ws, &ctx->splitk_ws_bytes, need, "split-K"));
+        p.splitk_ws = ctx->splitk_ws;
+    }
+    dim3 grid((unsigned)(p.tiles_m * p.tiles_n), (unsigned)p.splits);
+    kernel<<<grid, C_::kThreads, C_::kSmemBytes, ctx->compute>>>(tmA, tmB, p);
+    RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma"));
+    if (p.splits > 1) {
+        long long total = a.M * a.N;
+        int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
+        splitk_reduce_kernel<<<blocks, 256, 0, ctx->compute>>>(p);
+        RST_TRY(after_launch(ctx, "splitk_reduce_kernel"));
+    }
+    return RST_OK;
+}
+
+template <bool A_K, bool B_K>
+int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p) {
+    const long long k_tiles = (a.K + kBK - 1) / kBK;
+    const long long tiles_large = ((a.M + 127) / 128) * ((a.N + 127) / 128);
+    if (tiles_large >= ctx->num_sms) return launch_cfg<128, 128, 2, 4, 6, A_K, B_K>(ctx, a, p, 1);
+    // Small problems: 64x64 tiles, and split K until the grid covers the GPU
+    // about twice, keeping at least four k-tiles per split.
+    const long long tiles_small = ((a.M + 63) / 64) * ((a.N + 63) / 64);
+    long long splits = 1;
+    if (tiles_small < 2LL * ctx->num_sms) {
+        splits = (2LL * ctx->num_sms + tiles_small - 1) / tiles_small;
+        splits = std::min(splits, std::max(1LL, k_tiles / 4));
+        splits = std::min(splits, 64LL);
+    }
+    return launch_cfg<64, 64, 2, 2, 4, A_K, B_K>(ctx, a, p, (int)splits);
+}
+
+}  // namespace
+
+int launch_gemm(rst_ctx* ctx, const GemmArgs& a) {
+    if (a.M == 0 || a.N == 0) return RST_OK;
+    if (a.M > 0x7fffff00LL || a.N > 0x7fffff00LL || a.K > 0x7fffff00LL)
+        return fail(ctx, RST_ERR_UNSUPPORTED, "GEMM extent beyond 2^31 (M %lld, N %lld, K %lld)", a.M, a.N, a.K);
+    GemmParams p{};
+    p.C = a.C; p.bias = a.bias; p.mask_src = a.mask_src; p.splitk_ws = nullptr;
+    p.status = ctx->d_status; p.divisor = a.divisor;
+    p.M = a.M; p.N = a.N; p.K = a.K; p.epilogue = a.epilogue; p.splits = 1;
+
+    // TMA needs 16-byte aligned bases and row pitches: the contiguous extent of
+    // each operand must be even.
+    const long long a_inner = a.a_kmajor ? a.K : a.M;
+    const long long b_inner = a.b_kmajor ? a.K : a.N;
+    const bool tma_ok = a.K > 0 && (a_inner % 2 == 0) && (b_inner % 2 == 0) &&
+                        (((uintptr_t)a.A | (uintptr_t)a.B) & 15u) == 0;
+    if (!tma_ok) {
+        long long sam = a.a_kmajor ? a.K : 1, sak = a.a_kmajor ? 1 : a.M;
+        long long sbk = a.b_kmajor ? 1 : a.N, sbn = a.b_kmajor ? a.K : 1;
+        long long total = a.M * a.N;
+        int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
+        gemm_f64_plain<<<blocks, 256, 0, ctx->compute>>>(a.A, a.B, sam, sak, sbk, sbn, p);
+        return after_launch(ctx, "gemm_f64_plain");
+    }
+    if (a.a_kmajor && a.b_kmajor) return launch_layout<true, true>(ctx, a, p);
+    if (a.a_kmajor && !a.b_kmajor) return launch_layout<true, false>(ctx, a, p);
+    if (!a.a_kmajor && !a.b_kmajor) return launch_layout<false, false>(ctx, a, p);
+    return fail(ctx, RST_ERR_UNSUPPORTED, "M-major A with K-major B is not implemented");
+}
+
+}  // namespace rst

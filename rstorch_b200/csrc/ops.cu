@@ -1,0 +1,232 @@
+// C-ABI entry points of the training-step operators: argument checks, shape
+// rules of the reference, and dispatch to the kernels.
+#include "common.h"
+
+using namespace rst;
+
+namespace {
+
+int need_ctx(const rst_ctx* c) {
+    if (!valid(c)) return fail(nullptr, RST_ERR_INVALID_ARG, "not a live context");
+    return RST_OK;
+}
+
+int same_shape(const rst_ctx* c, const rst_tensor* a, const rst_tensor* b, const char* what) {
+    if (a->rows != b->rows || a->cols != b->cols)
+        return fail(c, RST_ERR_SHAPE, "%s: (%lld,%lld) vs (%lld,%lld)", what, (long long)a->rows,
+                    (long long)a->cols, (long long)b->rows, (long long)b->cols);
+    return RST_OK;
+}
+
+}  // namespace
+
+// Y = X · Wᵀ + b, optional fused ReLU          (src/module/linear.rs:43-57, relu.rs:21)
+extern "C" int rst_linear_forward(rst_ctx* c, const rst_tensor* X, const rst_tensor* W,
+                                  const rst_tensor* b, int relu, rst_tensor* Y) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, W, "W"));
+    RST_TRY(check_tensor(c, Y, "Y"));
+    if (b) RST_TRY(check_tensor(c, b, "b"));
+    const int64_t B = X->rows, in = X->cols, out = W->rows;
+    if (W->cols != in)
+        return fail(c, RST_ERR_SHAPE, "Linear::forward: input (%lld,%lld) against weight (%lld,%lld)",
+                    (long long)B, (long long)in, (long long)out, (long long)W->cols);
+    if (b && b->rows * b->cols != out)
+        return fail(c, RST_ERR_SHAPE, "Linear::forward: bias has %lld elements, expected %lld",
+                    (long long)(b->rows * b->cols), (long long)out);
+    if (Y->rows != B || Y->cols != out)
+        return fail(c, RST_ERR_SHAPE, "Linear::forward: output is (%lld,%lld), expected (%lld,%lld)",
+                    (long long)Y->rows, (long long)Y->cols, (long long)B, (long long)out);
+    if (Y->data == X->data || Y->data == W->data)
+        return fail(c, RST_ERR_INVALID_ARG, "Linear::forward: output aliases an input");
+    GemmArgs g{};
+    g.A = X->data; g.B = W->data; g.C = Y->data;
+    g.M = B; g.N = out; g.K = in;
+    g.a_kmajor = true; g.b_kmajor = true;
+    g.bias = b ? b->data : nullptr;
+    g.epilogue = b ? (relu ? kEpiBiasRelu : kEpiBias) : kEpiNone;
+    g.divisor = 1.0;
+    {
+        ProfScope prof(c, "gemm_fwd");
+        RST_TRY(launch_gemm(c, g));
+    }
+    if (!b && relu) return launch_relu_forward(c, Y->data, Y->data, B * out);
+    return RST_OK;
+}
+
+// dW = dYᵀ·X / n, db = Σ_rows dY / n, dX = dY·W [* relu mask]   (src/module/linear.rs:60-69, relu.rs:26)
+extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X,
+                                   const rst_tensor* W, const rst_tensor* mask, rst_tensor* dW,
+                                   rst_tensor* db, rst_tensor* dX) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, dY, "dY"));
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, W, "W"));
+    RST_TRY(check_tensor(c, dW, "dW"));
+    if (db) RST_TRY(check_tensor(c, db, "db"));
+    if (dX) RST_TRY(check_tensor(c, dX, "dX"));
+    if (mask) RST_TRY(check_tensor(c, mask, "relu_mask_src"));
+    const int64_t B = X->rows, in = X->cols, out = W->rows;
+    if (W->cols != in || dY->rows != B || dY->cols != out)
+        return fail(c, RST_ERR_SHAPE,
+                    "Linear::backward: gradient (%lld,%lld), cached input (%lld,%lld), weight (%lld,%lld)",
+                    (long long)dY->rows, (long long)dY->cols, (long long)B, (long long)in,
+                    (long long)out, (long long)W->cols);
+    RST_TRY(same_shape(c, dW, W, "Linear::backward: dW against W"));
+    if (db && db->rows * db->cols != out)
+        return fail(c, RST_ERR_SHAPE, "Linear::backward: db has %lld elements, expected %lld",
+                    (long long)(db->rows * db->cols), (long long)out);
+    if (dX) RST_TRY(same_shape(c, dX, X, "Linear::backward: dX against X"));
+    if (mask && !dX) return fail(c, RST_ERR_INVALID_ARG, "relu_mask_src given without dX");
+    if (mask) RST_TRY(same_shape(c, mask, X, "Linear::backward: relu_mask_src against X"));
+    if (dX && (dX->data == dY->data || dX->data == W->data))
+        return fail(c, RST_ERR_INVALID_ARG, "Linear::backward: dX aliases an input");
+
+    const double n = (double)B;   // linear.rs:62
+    GemmArgs gw{};
+    gw.A = dY->data; gw.B = X->data; gw.C = dW->data;
+    gw.M = out; gw.N = in; gw.K = B;
+    gw.a_kmajor = false; gw.b_kmajor = false;
+    gw.epilogue = kEpiDivN; gw.divisor = n;
+    {
+        ProfScope prof(c, "gemm_dW");
+        RST_TRY(launch_gemm(c, gw));
+    }
+    if (db) {
+        ProfScope prof(c, "colsum");
+        RST_TRY(launch_colsum_div(c, dY->data, B, out, n, db->data));
+    }
+    if (dX) {
+        GemmArgs gx{};
+        gx.A = dY->data; gx.B = W->data; gx.C = dX->data;
+        gx.M = B; gx.N = in; gx.K = out;
+        gx.a_kmajor = true; gx.b_kmajor = false;
+        gx.epilogue = mask ? kEpiMask : kEpiNone;
+        gx.mask_src = mask ? mask->data : nullptr;
+        gx.divisor = 1.0;
+        ProfScope prof(c, "gemm_dX");
+        RST_TRY(launch_gemm(c, gx));
+    }
+    return RST_OK;
+}
+
+extern "C" int rst_relu_forward(rst_ctx* c, const rst_tensor* X, rst_tensor* Y) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, Y, "Y"));
+    RST_TRY(same_shape(c, X, Y, "ReLU::forward"));
+    ProfScope prof(c, "relu_fwd");
+    return launch_relu_forward(c, X->data, Y->data, X->rows * X->cols);
+}
+
+extern "C" int rst_relu_backward(rst_ctx* c, const rst_tensor* dY, const rst_tensor* Xpre,
+                                 rst_tensor* dX) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, dY, "dY"));
+    RST_TRY(check_tensor(c, Xpre, "X_pre"));
+    RST_TRY(check_tensor(c, dX, "dX"));
+    RST_TRY(same_shape(c, dY, Xpre, "ReLU::backward: gradient against cached input"));
+    RST_TRY(same_shape(c, dY, dX, "ReLU::backward: output"));
+    ProfScope prof(c, "relu_bwd");
+    return launch_relu_backward(c, dY->data, Xpre->data, dX->data, dY->rows * dY->cols);
+}
+
+extern "C" int rst_softmax(rst_ctx* c, const rst_tensor* X, rst_tensor* P) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, P, "P"));
+    RST_TRY(same_shape(c, X, P, "softmax"));
+    if (X->cols > 0x7fffffff) return fail(c, RST_ERR_UNSUPPORTED, "more than 2^31 columns");
+    return launch_softmax(c, X->data, P->data, X->rows, X->cols);
+}
+
+extern "C" int rst_xent_slots(void) { return kXentSlots; }
+
+extern "C" int rst_xent_forward_backward(rst_ctx* c, const rst_tensor* logits, const rst_tensor* truth,
+                                         rst_tensor* dlogits, int slot) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, logits, "logits"));
+    RST_TRY(check_tensor(c, truth, "truth"));
+    if (dlogits) RST_TRY(check_tensor(c, dlogits, "dlogits"));
+    if (slot < 0 || slot >= kXentSlots)
+        return fail(c, RST_ERR_INVALID_ARG, "slot %d out of range [0,%d)", slot, kXentSlots);
+    RST_TRY(same_shape(c, logits, truth, "CrossEntropyLoss::forward: pred against truth"));
+    if (dlogits) RST_TRY(same_shape(c, logits, dlogits, "CrossEntropyLoss::backward: output"));
+    if (logits->cols == 0) return fail(c, RST_ERR_SHAPE, "CrossEntropyLoss: zero classes");
+    if (logits->cols > 0x7fffffff) return fail(c, RST_ERR_UNSUPPORTED, "more than 2^31 columns");
+    {
+        ProfScope prof(c, "xent");
+        RST_TRY(launch_xent(c, logits->data, truth->data, dlogits ? dlogits->data : nullptr, logits->rows,
+                            logits->cols, c->d_results + slot));
+    }
+    RST_CUDA(c, cudaMemcpyAsync(c->h_results + slot, c->d_results + slot, sizeof(ResultSlot),
+                                cudaMemcpyDeviceToHost, c->compute));
+    if (c->capturing) {
+        c->result_pending[slot] = true;   // replayed by a graph: read after a stream sync
+        c->result_in_graph[slot] = true;
+    } else {
+        RST_CUDA(c, cudaEventRecord(c->result_event[slot], c->compute));
+        c->result_pending[slot] = true;
+        c->result_in_graph[slot] = false;
+    }
+    return RST_OK;
+}
+
+extern "C" int rst_xent_result(rst_ctx* c, int slot, double* loss, double* accuracy) {
+    RST_TRY(need_ctx(c));
+    if (slot < 0 || slot >= kXentSlots)
+        return fail(c, RST_ERR_INVALID_ARG, "slot %d out of range [0,%d)", slot, kXentSlots);
+    if (!c->result_pending[slot])
+        return fail(c, RST_ERR_STATE, "result slot %d was never written (forward not called)", slot);
+    if (c->capturing) return fail(c, RST_ERR_STATE, "blocking read during graph capture");
+    if (c->result_in_graph[slot]) RST_CUDA(c, cudaStreamSynchronize(c->compute));
+    else RST_CUDA(c, cudaEventSynchronize(c->result_event[slot]));
+    const ResultSlot r = c->h_results[slot];
+    // loss = -(Σ t·ln p) / B                               (src/loss/cross_entropy.rs:38)
+    if (loss) *loss = -r.loss_sum / r.rows;
+    // accuracy = correct / rows                             (src/utils.rs:59-64)
+    if (accuracy) *accuracy = r.correct / r.rows;
+    if (r.nan_rows > 0.0)
+        return fail(c, RST_ERR_NAN, "%lld row(s) of the logits hold NaN; the reference panics in softmax",
+                    (long long)r.nan_rows);
+    return RST_OK;
+}
+
+extern "C" int rst_argmax(rst_ctx* c, const rst_tensor* t, int64_t* idx) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, t, "t"));
+    if (c->capturing) return fail(c, RST_ERR_STATE, "blocking call during graph capture");
+    if (t->rows == 0) return RST_OK;
+    if (!idx) return fail(c, RST_ERR_INVALID_ARG, "idx is NULL");
+    if (t->cols == 0) return fail(c, RST_ERR_SHAPE, "argmax of rows with zero columns");
+    if (t->cols > 0x7fffffff) return fail(c, RST_ERR_UNSUPPORTED, "more than 2^31 columns");
+    rst_tensor* tmp = nullptr;   // rows int64 values fit a (rows,1) f64 block
+    RST_TRY(rst_tensor_alloc(c, t->rows, 1, &tmp));
+    int s = launch_argmax(c, t->data, t->rows, t->cols, reinterpret_cast<long long*>(tmp->data));
+    if (s == RST_OK) {
+        cudaError_t e = cudaMemcpyAsync(idx, tmp->data, (size_t)t->rows * sizeof(int64_t),
+                                        cudaMemcpyDeviceToHost, c->compute);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->compute);
+        if (e != cudaSuccess) s = fail(c, RST_ERR_CUDA, "argmax read-back failed: %s", cudaGetErrorString(e));
+    }
+    rst_tensor_free(tmp);
+    return s;
+}
+
+extern "C" int rst_accuracy(rst_ctx* c, const rst_tensor* pred, const rst_tensor* truth, double* acc) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, pred, "pred"));
+    RST_TRY(check_tensor(c, truth, "truth"));
+    if (!acc) return fail(c, RST_ERR_INVALID_ARG, "acc is NULL");
+    if (pred->rows != truth->rows)
+        return fail(c, RST_ERR_SHAPE, "accuracy: %lld predictions against %lld targets",
+                    (long long)pred->rows, (long long)truth->rows);
+    std::vector<int64_t> a((size_t)pred->rows), b((size_t)truth->rows);
+    RST_TRY(rst_argmax(c, pred, a.data()));
+    RST_TRY(rst_argmax(c, truth, b.data()));
+    int64_t hit = 0;
+    for (size_t i = 0; i < a.size(); ++i) hit += (a[i] == b[i]);
+    *acc = (double)hit / (double)pred->rows;
+    return RST_OK;
+}

@@ -1,0 +1,131 @@
+"""Batch assembly: `DataLoader::iter_array` (src/data/data_loader.rs:42-93,180-208)
+with the batches staged through pinned host memory and a copy stream."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Iterator
+
+import numpy as np
+
+from .core import Context, Tensor
+
+
+class ArrayDataset:
+    """Random-access dataset of (sample, target) rows held as two host arrays;
+    `get`/`len` follow the `Dataset` trait (src/data/dataset/mod.rs:15-57)."""
+
+    def __init__(self, samples: np.ndarray, targets: np.ndarray):
+        if len(samples) != len(targets):
+            raise ValueError("samples and targets differ in length")
+        self.samples = np.asarray(samples, dtype=np.float64).reshape(len(samples), -1)
+        self.targets = np.asarray(targets, dtype=np.float64).reshape(len(targets), -1)
+
+    def get(self, index: int):
+        if not 0 <= index < len(self.samples):
+            return None
+        return self.samples[index], self.targets[index]
+
+    def __len__(self) -> int:
+        return len(self.samples)
+
+
+class SequentialSampler:
+    """0..size (src/data/sampler.rs:31-43)."""
+
+    def __init__(self, size: int):
+        self.size = int(size)
+
+    def iter(self) -> Iterator[int]:
+        return iter(range(self.size))
+
+
+class DataLoader:
+    """`DataLoader::new(dataset, batch_size, shuffle, sampler)`.
+
+    `iter_array` yields `(X, T)` device tensors of `batch_size` consecutive sampler
+    indices and, like the reference, ends the epoch at the first batch it cannot
+    fill (the remainder is dropped, data_loader.rs:69-71,197).  The reference's
+    shuffle draws from an unseedable thread RNG (dataset/shuffler.rs:15-25); here
+    it is a permutation from `shuffle_seed`, redrawn at every `iter_array` call."""
+
+    def __init__(self, dataset: ArrayDataset, batch_size: int, shuffle: bool, sampler: SequentialSampler,
+                 ctx: Context, slots: int = 2, shuffle_seed: int = 0):
+        self.dataset, self.batch_size, self.sampler, self.ctx = dataset, int(batch_size), sampler, ctx
+        self._shuffle = bool(shuffle)
+        self._rng = np.random.default_rng(shuffle_seed)
+        self._slots = int(slots)
+        self._stager = None
+
+    def __len__(self) -> int:
+        return len(self.dataset) // self.batch_size
+
+    def is_empty(self) -> bool:
+        return len(self.dataset) < self.batch_size
+
+    # -- staging -------------------------------------------------------------
+    def _ensure_stager(self):
+        if self._stager is None:
+            h = C.c_void_p()
+            lib, ctx = self.ctx._lib, self.ctx
+            ctx._check(lib.rst_stager_create(ctx.handle, self.batch_size, self.dataset.samples.shape[1],
+                                             self.dataset.targets.shape[1], self._slots, C.byref(h)))
+            self._stager = h
+        return self._stager
+
+    def _host_views(self, slot: int):
+        lib, ctx = self.ctx._lib, self.ctx
+        px, pt = C.POINTER(C.c_double)(), C.POINTER(C.c_double)()
+        ctx._check(lib.rst_stager_host(self._stager, slot, C.byref(px), C.byref(pt)))
+        b = self.batch_size
+        x = np.ctypeslib.as_array(px, shape=(b, self.dataset.samples.shape[1]))
+        t = np.ctypeslib.as_array(pt, shape=(b, self.dataset.targets.shape[1]))
+        return x, t
+
+    def _fill(self, slot: int, indices: np.ndarray) -> None:
+        x, t = self._host_views(slot)
+        np.take(self.dataset.samples, indices, axis=0, out=x)
+        np.take(self.dataset.targets, indices, axis=0, out=t)
+        self.ctx._check(self.ctx._lib.rst_stager_submit(self._stager, slot))
+
+    def _acquire(self, slot: int) -> tuple[Tensor, Tensor]:
+        lib, ctx = self.ctx._lib, self.ctx
+        hx, ht = C.c_void_p(), C.c_void_p()
+        ctx._check(lib.rst_stager_acquire(self._stager, slot, C.byref(hx), C.byref(ht)))
+        b = self.batch_size
+        # the stager owns these tensors; the wrappers must not free them
+        return (Tensor(ctx, hx, b, self.dataset.samples.shape[1], owns=False),
+                Tensor(ctx, ht, b, self.dataset.targets.shape[1], owns=False))
+
+    def iter_array(self) -> Iterator[tuple[Tensor, Tensor]]:
+        self._ensure_stager()
+        order = np.fromiter(self.sampler.iter(), dtype=np.int64)
+        if self._shuffle:
+            perm = self._rng.permutation(len(self.dataset))
+            order = perm[order]
+        order = order[order < len(self.dataset)] if (order >= len(self.dataset)).any() else order
+        n_batches = len(order) // self.batch_size
+        b = self.batch_size
+        # keep `slots - 1` batches in flight ahead of the one being consumed
+        ahead = min(self._slots - 1, n_batches) if self._slots > 1 else 0
+        for k in range(ahead):
+            self._fill(k % self._slots, order[k * b:(k + 1) * b])
+        for k in range(n_batches):
+            slot = k % self._slots
+            if self._slots == 1:
+                self._fill(slot, order[k * b:(k + 1) * b])
+            yield self._acquire(slot)
+            nxt = k + ahead
+            if self._slots > 1 and nxt < n_batches:
+                # the slot consumed one iteration ago is free again
+                self._fill(nxt % self._slots, order[nxt * b:(nxt + 1) * b])
+
+    def close(self) -> None:
+        if self._stager is not None and self.ctx.handle.value:
+            self.ctx._lib.rst_stager_destroy(self._stager)
+        self._stager = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,369 @@
+"""Parity of every kernel, called through the C ABI, with the CPU restatement."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import rstorch_b200 as rt
+from conftest import REL_TOL, rel_err
+from rstorch_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def A(x):
+    return np.array(x, dtype=np.float64)
+
+
+class Fixed(rt.InitParameters):
+    def __init__(self, w, b):
+        self.w, self.b = A(w), A(b)
+
+    def weight(self, i, o):
+        return self.w
+
+    def bias(self, i, o):
+        return self.b
+
+
+# ---- the reference's own unit tests, through the device path -------------------------
+def test_kat_linear_forward(ctx, kat):
+    k = kat["linear_forward"]
+    m = rt.Linear.new_with_kernel(2, 1, Fixed(k["weight"], k["bias"]))
+    y = m.forward(ctx.tensor(A(k["input"]))).numpy()
+    assert np.max(np.abs(y - A(k["expected"]))) <= kat["tolerance"]
+
+
+def test_kat_linear_backward(ctx, kat):
+    k = kat["linear_backward"]
+    m = rt.Linear.new_with_kernel(2, 1, Fixed(k["weight"], k["bias"]))
+    m.forward(ctx.tensor(A(k["input"])))
+    dx = m.backward(ctx.tensor(A(k["gradient"]))).numpy()
+    assert m.grad_weight.shape == m.weight.shape and m.grad_bias.shape == m.bias.shape
+    tol = kat["tolerance"]
+    assert np.max(np.abs(m.grad_weight.numpy() - A(k["expected_grad_weight"]))) <= tol
+    assert np.max(np.abs(m.grad_bias.numpy() - A(k["expected_grad_bias"]))) <= tol
+    assert np.max(np.abs(dx - A(k["expected_grad_input"]))) <= tol
+
+
+def test_kat_relu_identity(ctx, kat):
+    f, b, i = kat["relu_forward"], kat["relu_backward"], kat["identity"]
+    m = rt.ReLU()
+    assert np.array_equal(m.forward(ctx.tensor(A(f["input"]))).numpy(), A(f["expected"]))
+    m.forward(ctx.tensor(A(b["input"])))
+    assert np.array_equal(m.backward(ctx.tensor(A(b["gradient"]))).numpy(), A(b["expected"]))
+    ident = rt.Identity()
+    x = ctx.tensor(A(i["input"]))
+    assert np.array_equal(ident.forward(x).numpy(), A(i["expected"]))
+    assert np.array_equal(ident.backward(x).numpy(), A(i["expected"]))
+
+
+def test_kat_softmax_rows(ctx, kat):
+    k = kat["softmax_rows_sum_to_one"]
+    x = ctx.tensor(A(k["input"]))
+    p = ctx.empty(3, 2)
+    ctx._check(ctx._lib.rst_softmax(ctx.handle, x.handle, p.handle))
+    p = p.numpy()
+    assert np.max(np.abs(p.sum(axis=1) - 1.0)) <= kat["tolerance"]
+    assert abs(p.sum() - 3.0) <= 4 * np.finfo(float).eps
+
+
+def test_kat_sgd_zero_gradient(ctx, kat):
+    lin = rt.Linear(2, 2, ctx=ctx)
+    w0 = lin.weight.numpy()
+    lin.forward(ctx.zeros(2, 2))
+    lin.backward(ctx.zeros(2, 2))
+    rt.SGD.new(kat["sgd_zero_gradient"]["lr"]).step(lin)
+    assert np.array_equal(lin.weight.numpy(), w0)
+
+
+# ---- Linear: all three GEMM layouts, every dispatch path -------------------------------
+LINEAR_SHAPES = [
+    (1, 2, 2),          # smallest TMA-addressable shape
+    (3, 5, 7),          # odd pitches: plain-load kernel
+    (32, 784, 100),     # C1 layer 1 (split-K forward)
+    (32, 100, 10),      # C1 head
+    (64, 100, 100),
+    (257, 130, 66),     # ragged in every dimension, 64x64 tiles
+    (4096, 784, 100),   # C2 layer 1 (split-K dW)
+    (2048, 1024, 2048), # 128x128 tiles, >= 148 of them
+    (1920, 272, 1288),  # 128x128 tiles with ragged edges in M, N and K
+]
+
+
+@pytest.mark.parametrize("B,cin,cout", LINEAR_SHAPES)
+def test_linear_forward_backward_parity(ctx, oc, B, cin, cout):
+    rng = np.random.default_rng(B + 7 * cin + 13 * cout)
+    X = rng.standard_normal((B, cin))
+    X[X < -0.5] = 0.0                                  # exact zeros as a ReLU output has
+    W, b = rng.standard_normal((cout, cin)) / np.sqrt(cin), rng.standard_normal((1, cout))
+    dY = rng.standard_normal((B, cout))
+    lin = rt.Linear.new_with_kernel(cin, cout, Fixed(W, b))
+    xd = ctx.tensor(X)
+
+    y = lin.forward(xd).numpy()
+    assert rel_err(y, oc.linear_forward(X, W, b)) < REL_TOL
+    dx = lin.backward(ctx.tensor(dY)).numpy()
+    dW, db, dX = oc.linear_backward(dY, X, W)
+    assert rel_err(lin.grad_weight.numpy(), dW) < REL_TOL
+    assert rel_err(lin.grad_bias.numpy(), db) < REL_TOL
+    assert rel_err(dx, dX) < REL_TOL
+
+    # fused epilogues: ReLU in forward, ReLU mask (from the cached input) in dX, dX skipped
+    y_relu = lin._forward(xd, fuse_relu=True).numpy()
+    assert np.array_equal(y_relu, np.maximum(y, 0.0))
+    dx_masked = lin._backward(ctx.tensor(dY), relu_mask=True, need_input_grad=True).numpy()
+    assert np.array_equal(dx_masked, dx * (X > 0.0))
+    lin._forward(xd, fuse_relu=False)
+    assert lin._backward(ctx.tensor(dY), relu_mask=False, need_input_grad=False) is None
+    assert rel_err(lin.grad_weight.numpy(), dW) < REL_TOL
+    ctx.check_device()
+
+
+def test_linear_is_deterministic_run_to_run(ctx):
+    rng = np.random.default_rng(0)
+    X, W, b = rng.standard_normal((512, 300)), rng.standard_normal((200, 300)), rng.standard_normal((1, 200))
+    lin = rt.Linear.new_with_kernel(300, 200, Fixed(W, b))
+    xd, gd = ctx.tensor(X), ctx.tensor(rng.standard_normal((512, 200)))
+    outs = []
+    for _ in range(3):
+        y = lin.forward(xd).numpy()
+        dx = lin.backward(gd).numpy()
+        outs.append((y, dx, lin.grad_weight.numpy(), lin.grad_bias.numpy()))
+    for o in outs[1:]:
+        for a, b_ in zip(o, outs[0]):
+            assert np.array_equal(a, b_)
+
+
+def test_linear_shape_errors(ctx):
+    lin = rt.Linear(4, 3, ctx=ctx)
+    with pytest.raises(rt.RstError) as e:
+        lin.forward(ctx.zeros(2, 5))
+    assert e.value.status == _lib.RST_ERR_SHAPE
+    lin.forward(ctx.zeros(2, 4))
+    with pytest.raises(rt.RstError) as e:
+        lin.backward(ctx.zeros(2, 4))
+    assert e.value.status == _lib.RST_ERR_SHAPE
+    other = rt.Context(0)
+    try:
+        mine, theirs = ctx.zeros(2, 4), other.zeros(2, 4)
+        st = ctx._lib.rst_relu_forward(ctx.handle, theirs.handle, mine.handle)
+        assert st == _lib.RST_ERR_FOREIGN_HANDLE
+        theirs.free()
+    finally:
+        other.close()
+
+
+# ---- ReLU ------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(1, 1), (3, 7), (129, 1001), (4096, 100)])
+def test_relu_parity(ctx, oc, shape):
+    rng = np.random.default_rng(shape[0])
+    x = rng.standard_normal(shape)
+    x.flat[::7] = 0.0
+    x.flat[3::11] = -0.0
+    if x.size > 5:
+        x.flat[5] = np.nan
+    g = rng.standard_normal(shape)
+    m = rt.ReLU()
+    assert np.array_equal(m.forward(ctx.tensor(x)).numpy(), oc.relu_forward(x))
+    assert np.array_equal(m.backward(ctx.tensor(g)).numpy(), oc.relu_backward(g, x), equal_nan=True)
+
+
+# ---- softmax / cross-entropy / accuracy ---------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(1, 1), (5, 2), (32, 10), (4096, 10), (33, 17), (100, 32), (64, 100),
+                                       (31, 500), (256, 1000), (8, 1024), (5, 1500)])
+def test_xent_parity(ctx, oc, rows, cols):
+    rng = np.random.default_rng(rows * 31 + cols)
+    x = rng.standard_normal((rows, cols)) * 4
+    t = np.eye(cols)[rng.integers(0, cols, rows)]
+    # make ties and repeated maxima part of the input
+    if cols > 2:
+        x[0, 1] = x[0, 2] = x[0].max() + 1.0
+    loss_fn = rt.CrossEntropyLoss()
+    xd, td = ctx.tensor(x), ctx.tensor(t)
+    loss = loss_fn.forward(xd, td)
+    want_loss, p, _ = oc.xent_forward(x, t)
+    assert abs(loss - want_loss) <= REL_TOL * abs(want_loss)
+    assert rel_err(loss_fn.backward().numpy(), oc.xent_backward(p, t)) < REL_TOL
+    assert loss_fn.last_accuracy == oc.accuracy(x, t)                 # bit-exact
+    assert rt.accuracy(xd, td) == oc.accuracy(x, t)
+    assert np.array_equal(rt.argmax(xd), oc.argmax(x))
+    sm = ctx.empty(rows, cols)
+    ctx._check(ctx._lib.rst_softmax(ctx.handle, xd.handle, sm.handle))
+    assert rel_err(sm.numpy(), p) < REL_TOL
+
+
+def test_xent_soft_labels_and_underflow(ctx, oc):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((16, 10))
+    t = rng.random((16, 10))
+    t /= t.sum(axis=1, keepdims=True)                                  # soft labels are legal
+    lf = rt.CrossEntropyLoss()
+    loss = lf.forward(ctx.tensor(x), ctx.tensor(t))
+    want, p, _ = oc.xent_forward(x, t)
+    assert abs(loss - want) <= REL_TOL * abs(want)
+    # 0 * ln(0) = NaN, as in cross_entropy.rs:38
+    x2, t2 = np.array([[0.0, -800.0]]), np.array([[1.0, 0.0]])
+    assert np.isnan(oc.xent_forward(x2, t2)[0])
+    assert np.isnan(rt.CrossEntropyLoss().forward(ctx.tensor(x2), ctx.tensor(t2)))
+
+
+def test_xent_nan_logit_is_an_error_like_the_reference_panic(ctx):
+    x = np.zeros((4, 10))
+    x[2, 3] = np.nan
+    t = np.eye(10)[[0, 1, 2, 3]]
+    with pytest.raises(rt.RstError) as e:
+        rt.CrossEntropyLoss().forward(ctx.tensor(x), ctx.tensor(t))
+    assert e.value.status == _lib.RST_ERR_NAN
+
+
+def test_argmax_first_maximum_wins(ctx, oc):
+    x = np.array([[1.0, 3.0, 3.0, 2.0], [5.0, 5.0, 5.0, 5.0], [np.nan, 9.0, 1.0, 0.0],
+                  [1.0, np.nan, 7.0, 7.0], [-np.inf, -np.inf, np.nan, -np.inf]])
+    assert rt.argmax(ctx.tensor(x)).tolist() == oc.argmax(x).tolist() == [1, 0, 0, 2, 0]
+    wide = np.zeros((3, 1300))
+    wide[0, 1200] = wide[0, 77] = 2.0
+    wide[1, :] = -1.0
+    wide[2, 0] = np.nan
+    wide[2, 5] = 9.0
+    assert rt.argmax(ctx.tensor(wide)).tolist() == oc.argmax(wide).tolist() == [77, 0, 0]
+
+
+def test_result_slot_misuse(ctx):
+    loss, acc = C.c_double(), C.c_double()
+    st = ctx._lib.rst_xent_result(ctx.handle, 10_000, C.byref(loss), C.byref(acc))
+    assert st == _lib.RST_ERR_INVALID_ARG
+    fresh = rt.Context(0)
+    try:
+        st = fresh._lib.rst_xent_result(fresh.handle, 0, C.byref(loss), C.byref(acc))
+        assert st == _lib.RST_ERR_STATE
+    finally:
+        fresh.close()
+
+
+# ---- SGD -----------------------------------------------------------------------------------
+def test_sgd_multi_tensor_is_bit_exact(ctx, oc):
+    rng = np.random.default_rng(2)
+    sizes = [1, 2, 3, 4095, 4096, 4097, 8192 * 3 + 5, 100 * 784, 100, 10]
+    params = [rng.standard_normal((1, n)) * 0.02 for n in sizes]
+    grads = [rng.standard_normal((1, n)) * 1e-3 for n in sizes]
+    pd, gd = [ctx.tensor(p) for p in params], [ctx.tensor(g) for g in grads]
+    from rstorch_b200.core import handle_array
+    for step in range(2):
+        ctx._check(ctx._lib.rst_sgd_step(ctx.handle, len(pd), handle_array(pd), handle_array(gd), 0.01))
+        params = [oc.sgd_step(p, g, 0.01) for p, g in zip(params, grads)]
+    for got, want in zip(pd, params):
+        assert np.array_equal(got.numpy(), want)
+
+
+def test_sgd_on_unaligned_slices_of_one_arena(ctx, oc):
+    rng = np.random.default_rng(4)
+    sizes = [5, 4099, 3, 12288, 7]
+    total = sum(sizes)
+    P, G = rng.standard_normal((1, total)), rng.standard_normal((1, total))
+    pa, ga = ctx.tensor(P), ctx.tensor(G)
+    ps, gs, o = [], [], 0
+    for n in sizes:
+        ps.append(pa.slice(o, 1, n)); gs.append(ga.slice(o, 1, n)); o += n
+    from rstorch_b200.core import handle_array
+    ctx._check(ctx._lib.rst_sgd_step(ctx.handle, len(ps), handle_array(ps), handle_array(gs), 0.5))
+    assert np.array_equal(pa.numpy(), oc.sgd_step(P, G, 0.5))
+    with pytest.raises(rt.RstError) as e:
+        pa.slice(total - 1, 1, 2)
+    assert e.value.status == _lib.RST_ERR_SHAPE
+
+
+def test_sgd_shape_mismatch(ctx):
+    from rstorch_b200.core import handle_array
+    a, b = ctx.zeros(2, 3), ctx.zeros(3, 2)
+    st = ctx._lib.rst_sgd_step(ctx.handle, 1, handle_array([a]), handle_array([b]), 0.1)
+    assert st == _lib.RST_ERR_SHAPE
+
+
+# ---- allocator, staging, graph replay ---------------------------------------------------------
+def test_caching_allocator_reuses_blocks_and_honours_the_limit():
+    c = rt.Context(0)
+    try:
+        t = c.empty(1000, 1000)
+        s1 = c.memory_stats()
+        assert s1["in_use"] >= 8_000_000 and s1["driver_allocs"] == 1
+        p1 = t.data_ptr()
+        t.free()
+        u = c.empty(1000, 1000)
+        s2 = c.memory_stats()
+        assert u.data_ptr() == p1 and s2["cache_hits"] == 1 and s2["driver_allocs"] == 1
+        u.free()
+        c.empty_cache()
+        assert c.memory_stats()["reserved"] == 0
+        c.set_memory_limit(4 << 20)
+        with pytest.raises(rt.RstError) as e:
+            c.empty(1024, 1024)          # 8 MiB
+        assert e.value.status == _lib.RST_ERR_OOM
+        small = c.empty(256, 256)        # 512 KiB still fits
+        assert small.numel == 65536
+    finally:
+        c.close()
+
+
+def test_data_loader_iter_array_matches_the_reference_test(ctx, kat):
+    k = kat["data_loader_iter_array"]
+    n = k["samples"]
+    samples = np.repeat(np.arange(n, dtype=np.float64), 16).reshape(n, 4, 4)
+    targets = np.repeat(np.arange(n, dtype=np.float64), 4).reshape(n, 4)
+    ds = rt.ArrayDataset(samples, targets)
+    dl = rt.DataLoader(ds, k["batch_size"], False, rt.SequentialSampler(len(ds)), ctx, slots=2)
+    assert len(dl) == k["expected_len"]
+    batches = [(x.numpy(), t.numpy()) for x, t in dl.iter_array()]
+    assert len(batches) == 3                               # the 4 left-over samples are dropped
+    for i, (x, t) in enumerate(batches):
+        lo = i * 32
+        assert np.array_equal(x, samples[lo:lo + 32].reshape(32, 16))
+        assert np.array_equal(t, targets[lo:lo + 32])
+    dl1 = rt.DataLoader(ds, 32, False, rt.SequentialSampler(len(ds)), ctx, slots=1)
+    assert [x.numpy()[0, 0] for x, _ in dl1.iter_array()] == [0.0, 32.0, 64.0]
+    dl.close(); dl1.close()
+
+
+def test_graph_replay_reproduces_the_eager_step(ctx, oc):
+    from rstorch_b200 import synth
+    dims = [20, 16, 12, 5]
+    W = synth.mlp_weights(7, dims)
+
+    def build():
+        layers = [rt.Identity()]
+        for l, (w, b) in enumerate(W):
+            layers.append(rt.Linear.new_with_kernel(dims[l], dims[l + 1], Fixed(w, b)))
+            if l + 1 < len(W):
+                layers.append(rt.ReLU())
+        return rt.sequential(*layers).to(ctx)
+
+    X, T = synth.mnist_like(7, 0, 8 * 3, features=20, classes=5, zero_fraction=0.5)
+    xd, td = ctx.empty(8, 20), ctx.empty(8, 5)
+    loss_fn, opt = rt.CrossEntropyLoss(), rt.SGD.new(0.05)
+
+    def step(model, slot):
+        pred = model.forward(xd)
+        loss_fn.forward_async(pred, td, slot)
+        model.backward(loss_fn.backward(), need_input_grad=False)
+        opt.step(model)
+
+    eager, graphed = build(), build()
+    eager_losses = []
+    for s in range(3):
+        xd.upload(X[s * 8:(s + 1) * 8]); td.upload(T[s * 8:(s + 1) * 8])
+        step(eager, 1)
+        eager_losses.append(loss_fn.result(1)[0])
+    # capture on the second model: one eager warm-up step at lr 0 semantics is not needed
+    # because capture itself executes nothing; weights change only on replay
+    xd.upload(X[:8]); td.upload(T[:8])
+    with ctx.capture() as cap:
+        step(graphed, 2)
+    losses = []
+    for s in range(3):
+        xd.upload(X[s * 8:(s + 1) * 8]); td.upload(T[s * 8:(s + 1) * 8])
+        cap.graph.launch()
+        losses.append(loss_fn.result(2)[0])
+    assert losses == eager_losses
+    for a, b in zip(eager.parameters(), graphed.parameters()):
+        assert np.array_equal(a.parm.numpy(), b.parm.numpy())
+    cap.graph.destroy()

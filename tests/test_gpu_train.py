@@ -1,0 +1,147 @@
+"""Whole training steps through the public API against the CPU restatement: the
+committed golden steps, the README model on the MNIST-shaped stream, and
+size-independent properties at benchmark sizes."""
+import numpy as np
+import pytest
+
+import rstorch_b200 as rt
+from conftest import REL_TOL, rel_err
+from rstorch_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+class Fixed(rt.InitParameters):
+    def __init__(self, w, b):
+        self.w, self.b = w, b
+
+    def weight(self, i, o):
+        return self.w
+
+    def bias(self, i, o):
+        return self.b
+
+
+def build_mlp(ctx, dims, weights, identity=True):
+    layers = [rt.Identity()] if identity else []
+    for l, (w, b) in enumerate(weights):
+        layers.append(rt.Linear.new_with_kernel(dims[l], dims[l + 1], Fixed(w, b)))
+        if l + 1 < len(weights):
+            layers.append(rt.ReLU())
+    return rt.sequential(*layers).to(ctx)
+
+
+def linears(model):
+    return [l for l in model.layers if isinstance(l, rt.Linear)]
+
+
+def test_golden_steps(ctx, golden_steps):
+    g = golden_steps
+    dims = g["dims"].tolist()
+    L, B, steps, lr = len(dims) - 1, int(g["batch"]), int(g["steps"]), float(g["lr"])
+    model = build_mlp(ctx, dims, [(g[f"W0_{l}"], g[f"b0_{l}"]) for l in range(L)])
+    loss_fn, opt = rt.CrossEntropyLoss(), rt.SGD.new(lr)
+    for s in range(steps):
+        x, t = ctx.tensor(g["X"][s * B:(s + 1) * B]), ctx.tensor(g["T"][s * B:(s + 1) * B])
+        pred = model.forward(x)
+        loss = loss_fn.forward(pred, t)
+        acc = rt.accuracy(pred, t)
+        assert rel_err(pred.numpy(), g[f"logits_{s}"]) < REL_TOL
+        assert abs(loss - float(g[f"loss_{s}"])) <= REL_TOL * abs(float(g[f"loss_{s}"]))
+        assert acc == float(g[f"acc_{s}"]) == loss_fn.last_accuracy
+        model.backward(loss_fn.backward())
+        for l, lin in enumerate(linears(model)):
+            assert rel_err(lin.grad_weight.numpy(), g[f"dW_{s}_{l}"]) < REL_TOL
+            assert rel_err(lin.grad_bias.numpy(), g[f"db_{s}_{l}"]) < REL_TOL
+        opt.step(model)
+        for l, lin in enumerate(linears(model)):
+            assert rel_err(lin.weight.numpy(), g[f"W_{s}_{l}"]) < REL_TOL
+            assert rel_err(lin.bias.numpy(), g[f"b_{s}_{l}"]) < REL_TOL
+
+
+@pytest.mark.parametrize("batch,steps", [(32, 40), (4096, 4)])
+def test_readme_model_trajectory(ctx, oc, batch, steps):
+    """784-100-100-10, lr 0.01: every step's loss, accuracy, gradients and weights
+    against the restated step, both teacher-forced (same weights in) and free-running."""
+    dims = [784, 100, 100, 10]
+    X, T = synth.mnist_like(0, 0, batch * steps)
+    w_cpu = [(w.copy(), b.copy()) for w, b in synth.mlp_weights(0, dims)]
+    model = build_mlp(ctx, dims, w_cpu)
+    loss_fn, opt = rt.CrossEntropyLoss(), rt.SGD.new(0.01)
+    ds = rt.ArrayDataset(X, T)
+    dl = rt.DataLoader(ds, batch, False, rt.SequentialSampler(len(ds)), ctx, slots=3)
+    min_gap = np.inf
+    for s, (x, t) in enumerate(dl.iter_array()):
+        pred = model.forward(x)
+        loss = loss_fn.forward(pred, t)
+        acc = rt.accuracy(pred, t)
+        logits = pred.numpy()
+        model.backward(loss_fn.backward(), need_input_grad=False)
+        opt.step(model)
+        xb, tb = X[s * batch:(s + 1) * batch], T[s * batch:(s + 1) * batch]
+        losses, accs, grads = oc.mlp_train(dims, w_cpu, xb, tb, batch, 1, 0.01, skip_first_dx=True)
+        top2 = np.sort(logits, axis=1)[:, -2:]
+        min_gap = min(min_gap, float((top2[:, 1] - top2[:, 0]).min()))
+        assert abs(loss - losses[0]) <= REL_TOL * abs(losses[0]), s
+        assert acc == accs[0] == loss_fn.last_accuracy, (s, min_gap)
+        for l, lin in enumerate(linears(model)):
+            assert rel_err(lin.grad_weight.numpy(), grads[l][0]) < REL_TOL, (s, l)
+            assert rel_err(lin.grad_bias.numpy(), grads[l][1]) < REL_TOL, (s, l)
+            assert rel_err(lin.weight.numpy(), w_cpu[l][0]) < REL_TOL, (s, l)
+            assert rel_err(lin.bias.numpy(), w_cpu[l][1]) < REL_TOL, (s, l)
+    assert s == steps - 1
+    dl.close()
+    ctx.check_device()
+
+
+def test_fused_and_unfused_paths_agree(ctx):
+    """Calling the layers one by one (no peephole fusion) gives the same step as Sequential."""
+    dims = [64, 48, 40, 10]
+    W = synth.mlp_weights(3, dims)
+    X, T = synth.gaussian_batch(3, 0, 0, 96, 64, 10, 96)
+    fused, plain = build_mlp(ctx, dims, W), build_mlp(ctx, dims, W)
+    lf1, lf2 = rt.CrossEntropyLoss(), rt.CrossEntropyLoss()
+    x, t = ctx.tensor(X), ctx.tensor(T)
+    l1 = lf1.forward(fused.forward(x), t)
+    dx1 = fused.backward(lf1.backward())
+    h = x
+    for layer in plain.layers:
+        h = layer.forward(h)
+    l2 = lf2.forward(h, t)
+    g = lf2.backward()
+    for layer in reversed(plain.layers):
+        g = layer.backward(g)
+    assert l1 == l2
+    assert np.array_equal(dx1.numpy(), g.numpy())
+    for a, b in zip(fused.parameters(), plain.parameters()):
+        assert np.array_equal(a.grad.numpy(), b.grad.numpy())
+
+
+def test_wide_layer_sampled_entries_at_benchmark_size(ctx):
+    """8192 x 4096 x 4096 (the wide-MLP layer): a CPU restatement of the full product is
+    too slow, so random output entries are recomputed as long-double dot products, and the
+    linearity of the layer in its input is checked on the whole output."""
+    rng = np.random.default_rng(0)
+    B, cin, cout = 8192, 4096, 4096
+    X = synth.normal(synth.stream_key(0, "t.x"), B * cin).reshape(B, cin)
+    W = synth.normal(synth.stream_key(0, "t.w"), cout * cin, std=1 / 64).reshape(cout, cin)
+    b = np.zeros((1, cout))
+    lin = rt.Linear.new_with_kernel(cin, cout, Fixed(W, b))
+    xd = ctx.tensor(X)
+    y = lin.forward(xd).numpy()
+    dY = synth.normal(synth.stream_key(0, "t.g"), B * cout).reshape(B, cout)
+    dx = lin.backward(ctx.tensor(dY)).numpy()
+    dW = lin.grad_weight.numpy()
+    db = lin.grad_bias.numpy()
+    ld = np.longdouble
+    scale_y, scale_dx, scale_dw = np.abs(y).max(), np.abs(dx).max(), np.abs(dW).max()
+    for _ in range(64):
+        r, c, k = rng.integers(0, B), rng.integers(0, cout), rng.integers(0, cin)
+        assert abs(y[r, c] - float(np.dot(X[r].astype(ld), W[c].astype(ld)))) < REL_TOL * scale_y
+        assert abs(dx[r, k] - float(np.dot(dY[r].astype(ld), W[:, k].astype(ld)))) < REL_TOL * scale_dx
+        assert abs(dW[c, k] - float(np.dot(dY[:, c].astype(ld), X[:, k].astype(ld)) / B)) < REL_TOL * scale_dw
+    assert rel_err(db, dY.sum(axis=0, keepdims=True) / B) < REL_TOL
+    # linearity: forward(2x) == 2*forward(x) exactly (powers of two do not round), bias is zero
+    y2 = lin.forward(ctx.tensor(2.0 * X)).numpy()
+    assert np.array_equal(y2, 2.0 * y)
+    ctx.check_device()
