@@ -427,7 +427,7 @@ def sgd_arm(args) -> None:
     from rstorch_b200.core import handle_array
     rank, world, local, dist = init_distributed(args.gpus)
     ctx = rt.Context(local)
-    total = (1 << 30) // world
+    total = (1 << args.sgd_log2_params) // world
     sizes = synth.sgd_tensor_sizes(SEED + rank, total, 64)
     params, grads = [], []
     chunk = np.empty(max(sizes))
@@ -509,6 +509,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOAD_NAMES), default="c4")
+    ap.add_argument("--sgd-log2-params", type=int, default=30,
+                    help="workload c5 only: log2 of the parameter count (30 is the benchmark size; "
+                         "smaller values are for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

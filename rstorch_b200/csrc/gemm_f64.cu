@@ -218,6 +218,11 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) dmma_m16n8k8(acc[mt][nt], a[mt], b[nt]);
         }
+        // The stage is about to be rewritten by TMA (async proxy) after having been
+        // read with ordinary shared loads (generic proxy): every reader orders its
+        // reads against the async proxy before the warp releases the stage.  Without
+        // this fence, refilled stages were observed half-written on B200.
+        fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
     }
