@@ -127,6 +127,28 @@ int rst_linear_backward(rst_ctx* ctx, const rst_tensor* dY, const rst_tensor* X,
                         const rst_tensor* W, const rst_tensor* relu_mask_src,
                         rst_tensor* dW, rst_tensor* db, rst_tensor* dX);
 
+/* Bias gradient without any allocation: db[c] = (Σ_r dY[r,c]) / rows, the same
+ * value rst_linear_backward writes to db.  This entry point has no counterpart in
+ * the reference; it exists for hosts that cannot call cudaMalloc where they need
+ * the result: inside a stream-capture region, in a step with a hard latency
+ * budget (an allocation may synchronise the device), or when another allocator
+ * owns all device memory and hands this library raw pointers only.
+ *   - dY and db are raw device pointers of the GPU that is current on the calling
+ *     thread; `stream` is a cudaStream_t of that GPU (NULL = default stream).
+ *   - No context, no tensor handles, no cudaMalloc/cudaFree: the partial column
+ *     sums go to a fixed 2 MiB array inside the library's device image, which
+ *     every GPU that loads the library holds until the process exits.
+ *   - cols may be at most RST_BIAS_GRAD_NOALLOC_MAX_COLS; larger requests fail
+ *     with RST_ERR_UNSUPPORTED and a message naming the limit.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call outside any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents
+ *     (the kernels overwrite every entry they later read, so nothing needs
+ *     clearing).  Two calls whose kernels overlap on the GPU (different streams)
+ *     race on it: order them on one stream or with events. */
+#define RST_BIAS_GRAD_NOALLOC_MAX_COLS 262144
+int rst_bias_grad_noalloc(const double* dY, int64_t rows, int64_t cols, double* db, void* stream);
+
 /* ---- ReLU, unfused (src/module/activation/relu.rs:17-32) ----------------- */
 int rst_relu_forward(rst_ctx* ctx, const rst_tensor* X, rst_tensor* Y);
 /* dX = dY * (X_pre > 0 ? 1 : 0); X_pre is the tensor ReLU::forward cached. */

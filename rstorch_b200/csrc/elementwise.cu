@@ -163,3 +163,94 @@ int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols
 }
 
 }  // namespace rst
+
+// ---------------------------------------------------------------------------
+// Bias gradient for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need
+// db: code running inside a stream-capture region (an allocation there fails or
+// invalidates the capture), a step function with a hard latency budget (cudaMalloc
+// may synchronise the whole device), or a process whose device memory is fully
+// owned by another allocator and handed out as raw pointers.  The regular path
+// grows its column-sum scratch from the driver on demand; this entry point uses a
+// fixed array that lives in the library's device image instead, so every GPU that
+// loads the library holds kNoAllocScratchDoubles * 8 bytes (2 MiB) until exit.
+// ---------------------------------------------------------------------------
+namespace rst {
+namespace {
+
+constexpr int64_t kNoAllocScratchDoubles = (int64_t)1 << 18;   // 2 MiB of partial column sums
+constexpr int kNoAllocMaxDevices = 64;
+
+static __device__ __align__(256) double g_noalloc_colsum_scratch[kNoAllocScratchDoubles];
+
+// Host code cannot use the array's name as a device address (it names a host-side
+// shadow symbol); the device address is looked up once per device.
+std::mutex g_noalloc_mutex;
+double* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {nullptr};
+
+int noalloc_scratch_for_current_device(double** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return fail(nullptr, RST_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kNoAllocMaxDevices)
+        return fail(nullptr, RST_ERR_UNSUPPORTED, "device ordinal %d beyond %d", dev, kNoAllocMaxDevices);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_scratch_ptr[dev]) {
+        double* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_colsum_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail(nullptr, RST_ERR_CUDA, "cudaGetSymbolAddress of the static scratch failed on device %d: %s",
+                        dev, cudaGetErrorString(e));
+        }
+        g_noalloc_scratch_ptr[dev] = p;
+    }
+    *out = g_noalloc_scratch_ptr[dev];
+    return RST_OK;
+}
+
+}  // namespace
+}  // namespace rst
+
+extern "C" int rst_bias_grad_noalloc(const double* dY, int64_t rows, int64_t cols, double* db, void* stream) {
+    using namespace rst;
+    if (rows < 0 || cols < 0) return fail(nullptr, RST_ERR_INVALID_ARG, "negative shape (%lld,%lld)",
+                                          (long long)rows, (long long)cols);
+    if (cols == 0) return RST_OK;
+    if (!db || (rows > 0 && !dY)) return fail(nullptr, RST_ERR_INVALID_ARG, "dY or db is NULL");
+    if (cols > kNoAllocScratchDoubles)
+        return fail(nullptr, RST_ERR_UNSUPPORTED,
+                    "rst_bias_grad_noalloc: %lld columns exceed the static scratch of %lld columns; "
+                    "use rst_linear_backward, which may allocate",
+                    (long long)cols, (long long)kNoAllocScratchDoubles);
+    double* scratch = nullptr;
+    RST_TRY(noalloc_scratch_for_current_device(&scratch));
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    // as many row parts as fit the fixed scratch, up to about four waves of blocks
+    const int64_t col_blocks = (cols + kColsPerBlock - 1) / kColsPerBlock;
+    int64_t parts = (148 * 4 + col_blocks - 1) / col_blocks;
+    const int64_t fit = kNoAllocScratchDoubles / cols;          // >= 1 by the check above
+    if (parts > fit) parts = fit;
+    const int64_t by_rows = (rows + 63) / 64;
+    if (parts > by_rows) parts = by_rows;
+    if (parts < 1) parts = 1;
+    if (parts > 65535) parts = 65535;
+    int64_t rows_per = (rows + parts - 1) / parts;
+    if (rows_per < 1) rows_per = 1;
+    parts = rows == 0 ? 1 : (rows + rows_per - 1) / rows_per;
+
+    // pass 1 writes every scratch entry that pass 2 reads, so nothing has to be
+    // cleared between calls
+    dim3 g1((unsigned)col_blocks, (unsigned)parts);
+    colsum_pass1<<<g1, kThreads, 0, st>>>(dY, rows, cols, rows_per, scratch);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(nullptr, RST_ERR_CUDA, "launch of colsum_pass1 failed: %s", cudaGetErrorString(e));
+    const int g2 = (int)((cols + kThreads - 1) / kThreads);
+    colsum_pass2<<<g2, kThreads, 0, st>>>(scratch, (int)parts, cols, (double)rows, db);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(nullptr, RST_ERR_CUDA, "launch of colsum_pass2 failed: %s", cudaGetErrorString(e));
+    return RST_OK;
+}
