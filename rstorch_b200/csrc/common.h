@@ -151,8 +151,10 @@ struct GemmArgs {
     const double* bias;       // [N]          (kEpiBias, kEpiBiasRelu)
     const double* mask_src;   // [M,N]        (kEpiMask)
     double divisor;           // n            (kEpiDivN)
+    double* colsum_out;       // optional [M]: Σ_k A(m,k) / divisor when A is M-major (db)
 };
-int launch_gemm(rst_ctx* ctx, const GemmArgs& a);
+// *colsum_done (optional) tells whether colsum_out was produced by the GEMM kernel itself.
+int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done = nullptr);
 
 int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols, double n,
                       double* out);

@@ -32,7 +32,8 @@ struct GemmParams {
     double* C;
     const double* bias;
     const double* mask_src;
-    double* splitk_ws;      // [splits][M][N] raw partial sums when splits > 1
+    double* splitk_ws;      // [splits][M][N] raw partial sums when splits > 1, then [splits][M] column sums
+    double* colsum_out;     // [M]: Σ_k A(m,k) / divisor, fused into the M-major-A kernel (db of Linear::backward)
     int* status;
     double divisor;
     long long M, N, K;
@@ -70,7 +71,7 @@ struct Cfg {
     static constexpr bool kMnNatural = !A_K && !B_K;
 };
 
-template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
 __global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
 gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const GemmParams p) {
@@ -158,6 +159,14 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.0;
 
+    // Column sums of the M-major A operand (db = Σ_rows dY / n, linear.rs:65-67): the
+    // warps of the first tile column that hold the A fragments anyway add them up.
+    static_assert(!FUSE_COLSUM || !A_K, "column sums are taken from an M-major A operand");
+    const bool do_colsum = FUSE_COLSUM && p.colsum_out != nullptr && tile_n == 0 && wn == 0;
+    double asum[FUSE_COLSUM ? MT : 1][2];
+#pragma unroll
+    for (int mt = 0; mt < (FUSE_COLSUM ? MT : 1); ++mt) asum[mt][0] = asum[mt][1] = 0.0;
+
     // Per-thread byte offsets inside a stage that do not depend on the k sub-step.
     // K-major operand: row*128, chunk (2t+i) ^ (row%8) with row%8 == g.
     const uint32_t a_row_off = (uint32_t)(wm * C_::WTM + g) * kRowBytes;          // + mt*16*128 (+8 rows: +1024)
@@ -175,7 +184,7 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!mbar_wait_bounded(full_bar(s), ph)) {
             atomicExch(p.status, kDevBarrierTimeout);
             atomicExch(p.status + 1, 2);
-            ok = false;
+            ok = false;     // results are invalid; keep going so that barriers and counters stay consistent
             break;
         }
         const uint32_t As = smem_base + (uint32_t)s * C_::kStageBytes;
@@ -202,6 +211,15 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     lds128(a[mt][2], a[mt][3], box + mn_off1);        // k = t+4
                 }
             }
+            if (FUSE_COLSUM) {
+                if (do_colsum) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        asum[mt][0] += a[mt][0] + a[mt][2];           // m = 2g
+                        asum[mt][1] += a[mt][1] + a[mt][3];           // m = 2g+1
+                    }
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 if (B_K) {
@@ -226,43 +244,96 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
     }
-    if (!ok) return;
 
     // ---------------- epilogue: registers -> global ----------------
-    const bool raw = p.splits > 1;
-    double* out = raw ? p.splitk_ws + (long long)split * p.M * p.N : p.C;
+    // Coordinates of accumulator element (mt, h, nt, e): h selects logical row g or g+8.
+    auto row_of = [&](int mt, int h) -> long long {
+        return m0 + wm * C_::WTM + mt * 16 + (A_K ? (g + 8 * h) : (2 * g + h));
+    };
+    auto col_of = [&](int nt, int e) -> long long {
+        if (B_K) return n0 + wn * C_::WTN + nt * 8 + 2 * t + e;
+        return n0 + wn * C_::WTN + (nt & ~1) * 8 + 4 * t + 2 * e + (nt & 1);
+    };
+    if (FUSE_COLSUM) {
+        if (do_colsum) {      // warp-uniform: add the four lanes that share g
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            // logical row g (h = 0) or g+8 (h = 1) of this m-tile
-            const long long r = m0 + wm * C_::WTM + mt * 16 + (A_K ? (g + 8 * h) : (2 * g + h));
-            if (r >= p.M) continue;
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    long long c;
-                    if (B_K) c = n0 + wn * C_::WTN + nt * 8 + 2 * t + e;
-                    else c = n0 + wn * C_::WTN + (nt & ~1) * 8 + 4 * t + 2 * e + (nt & 1);
-                    if (c >= p.N) continue;
-                    double v = acc[mt][nt][2 * h + e];
-                    if (!raw) v = apply_epilogue(p, v, r, c);
-                    out[r * p.N + c] = v;
+                for (int h = 0; h < 2; ++h) {
+                    double v = asum[mt][h];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    asum[mt][h] = v;
                 }
-            }
         }
     }
+
+    const long long MN = p.M * p.N;
+    if (p.splits == 1) {
+        if (ok) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const long long r = row_of(mt, h);
+                    if (r >= p.M) continue;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const long long c = col_of(nt, e);
+                            if (c < p.N) p.C[r * p.N + c] = apply_epilogue(p, acc[mt][nt][2 * h + e], r, c);
+                        }
+                    if (FUSE_COLSUM) {
+                        if (do_colsum && t == 0) p.colsum_out[r] = asum[mt][h] / p.divisor;
+                    }
+                }
+        }
+        return;
+    }
+
+    // Split-K: every split stores its raw partial tile (and partial column sums);
+    // splitk_reduce_kernel adds them in split order and applies the epilogue.
+    double* part = p.splitk_ws + (long long)split * MN;
+    double* colpart = p.splitk_ws + (long long)p.splits * MN;            // [splits][M]
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const long long r = row_of(mt, h);
+            if (r >= p.M) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const long long c = col_of(nt, e);
+                    if (c < p.N) part[r * p.N + c] = acc[mt][nt][2 * h + e];
+                }
+            if (FUSE_COLSUM) {
+                if (do_colsum && t == 0) colpart[(long long)split * p.M + r] = asum[mt][h];
+            }
+        }
 }
 
-// Sums the split-K partials in split order and applies the epilogue.
+// Sums the split-K partials in split order and applies the epilogue; elements past
+// M*N are the fused column sums (db).
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
-    const long long total = p.M * p.N;
+    const long long MN = p.M * p.N;
+    const long long total = MN + (p.colsum_out ? p.M : 0);
     const long long stride = (long long)gridDim.x * blockDim.x;
+    const double* colpart = p.splitk_ws + (long long)p.splits * MN;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         double v = 0.0;
-        for (int z = 0; z < p.splits; ++z) v += p.splitk_ws[(long long)z * total + i];
-        p.C[i] = apply_epilogue(p, v, i / p.N, i % p.N);
+        if (i < MN) {
+#pragma unroll 4
+            for (int z = 0; z < p.splits; ++z) v += p.splitk_ws[(long long)z * MN + i];
+            p.C[i] = apply_epilogue(p, v, i / p.N, i % p.N);
+        } else {
+            const long long m = i - MN;
+#pragma unroll 4
+            for (int z = 0; z < p.splits; ++z) v += colpart[(long long)z * p.M + m];
+            p.colsum_out[m] = v / p.divisor;
+        }
     }
 }
 
@@ -297,10 +368,10 @@ int encode_map(rst_ctx* ctx, CUtensorMap* map, const double* base, long long inn
     return RST_OK;
 }
 
-template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
 int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
-    auto kernel = gemm_f64_tma_dmma<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
+    auto kernel = gemm_f64_tma_dmma<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM>;
     static bool attr_set[16] = {false};   // per device
     if (!attr_set[ctx->device & 15]) {
         RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes));
@@ -320,16 +391,17 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     if (p.k_tiles_per_split < 1) p.k_tiles_per_split = 1;
     p.splits = std::max(1, (p.k_tiles + p.k_tiles_per_split - 1) / p.k_tiles_per_split);
     if (p.splits > 1) {
-        size_t need = (size_t)p.splits * (size_t)a.M * (size_t)a.N * sizeof(double);
+        size_t need = (size_t)p.splits * ((size_t)a.M * (size_t)a.N + (size_t)a.M) * sizeof(double);
         RST_TRY(ensure_scratch(ctx, (void**)&ctx->splitk_ws, &ctx->splitk_ws_bytes, need, "split-K"));
         p.splitk_ws = ctx->splitk_ws;
     }
+    p.colsum_out = FUSE_COLSUM ? a.colsum_out : nullptr;
     dim3 grid((unsigned)(p.tiles_m * p.tiles_n), (unsigned)p.splits);
     kernel<<<grid, C_::kThreads, C_::kSmemBytes, ctx->compute>>>(tmA, tmB, p);
     RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma"));
     if (p.splits > 1) {
-        long long total = a.M * a.N;
-        int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
+        const long long total = a.M * a.N + (p.colsum_out ? a.M : 0);
+        const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
         splitk_reduce_kernel<<<blocks, 256, 0, ctx->compute>>>(p);
         RST_TRY(after_launch(ctx, "splitk_reduce_kernel"));
     }
@@ -337,30 +409,34 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
 }
 
 template <bool A_K, bool B_K>
-int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p) {
+int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_done) {
     const long long k_tiles = (a.K + kBK - 1) / kBK;
     const long long tiles_large = ((a.M + 127) / 128) * ((a.N + 127) / 128);
-    if (tiles_large >= ctx->num_sms) return launch_cfg<128, 128, 2, 4, 6, A_K, B_K>(ctx, a, p, 1);
-    // Small problems: 64x64 tiles, and split K until the grid covers the GPU
-    // about twice, keeping at least four k-tiles per split.
+    if (tiles_large >= ctx->num_sms) return launch_cfg<128, 128, 2, 4, 6, A_K, B_K, false>(ctx, a, p, 1);
+    // Small problems: 64x64 tiles, and split K until the grid covers the GPU about
+    // twice, keeping at least four k-tiles per split and at most 16 splits.
     const long long tiles_small = ((a.M + 63) / 64) * ((a.N + 63) / 64);
     long long splits = 1;
     if (tiles_small < 2LL * ctx->num_sms) {
         splits = (2LL * ctx->num_sms + tiles_small - 1) / tiles_small;
         splits = std::min(splits, std::max(1LL, k_tiles / 4));
-        splits = std::min(splits, 64LL);
+        splits = std::min(splits, 16LL);
     }
-    return launch_cfg<64, 64, 2, 2, 4, A_K, B_K>(ctx, a, p, (int)splits);
+    constexpr bool kFuse = !A_K && !B_K;     // the dW product also yields db
+    if (kFuse && a.colsum_out && colsum_done) *colsum_done = true;
+    return launch_cfg<64, 64, 2, 2, 4, A_K, B_K, kFuse>(ctx, a, p, (int)splits);
 }
 
 }  // namespace
 
-int launch_gemm(rst_ctx* ctx, const GemmArgs& a) {
+int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done) {
+    if (colsum_done) *colsum_done = false;
     if (a.M == 0 || a.N == 0) return RST_OK;
     if (a.M > 0x7fffff00LL || a.N > 0x7fffff00LL || a.K > 0x7fffff00LL)
         return fail(ctx, RST_ERR_UNSUPPORTED, "GEMM extent beyond 2^31 (M %lld, N %lld, K %lld)", a.M, a.N, a.K);
     GemmParams p{};
     p.C = a.C; p.bias = a.bias; p.mask_src = a.mask_src; p.splitk_ws = nullptr;
+    p.colsum_out = nullptr;
     p.status = ctx->d_status; p.divisor = a.divisor;
     p.M = a.M; p.N = a.N; p.K = a.K; p.epilogue = a.epilogue; p.splits = 1;
 
@@ -378,9 +454,9 @@ int launch_gemm(rst_ctx* ctx, const GemmArgs& a) {
         gemm_f64_plain<<<blocks, 256, 0, ctx->compute>>>(a.A, a.B, sam, sak, sbk, sbn, p);
         return after_launch(ctx, "gemm_f64_plain");
     }
-    if (a.a_kmajor && a.b_kmajor) return launch_layout<true, true>(ctx, a, p);
-    if (a.a_kmajor && !a.b_kmajor) return launch_layout<true, false>(ctx, a, p);
-    if (!a.a_kmajor && !a.b_kmajor) return launch_layout<false, false>(ctx, a, p);
+    if (a.a_kmajor && a.b_kmajor) return launch_layout<true, true>(ctx, a, p, colsum_done);
+    if (a.a_kmajor && !a.b_kmajor) return launch_layout<true, false>(ctx, a, p, colsum_done);
+    if (!a.a_kmajor && !a.b_kmajor) return launch_layout<false, false>(ctx, a, p, colsum_done);
     return fail(ctx, RST_ERR_UNSUPPORTED, "M-major A with K-major B is not implemented");
 }
 

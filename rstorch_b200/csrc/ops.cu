@@ -89,11 +89,13 @@ extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_t
     gw.M = out; gw.N = in; gw.K = B;
     gw.a_kmajor = false; gw.b_kmajor = false;
     gw.epilogue = kEpiDivN; gw.divisor = n;
+    gw.colsum_out = db ? db->data : nullptr;
+    bool db_done = false;
     {
         ProfScope prof(c, "gemm_dW");
-        RST_TRY(launch_gemm(c, gw));
+        RST_TRY(launch_gemm(c, gw, &db_done));
     }
-    if (db) {
+    if (db && !db_done) {
         ProfScope prof(c, "colsum");
         RST_TRY(launch_colsum_div(c, dY->data, B, out, n, db->data));
     }

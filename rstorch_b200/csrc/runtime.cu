@@ -320,6 +320,8 @@ extern "C" int rst_ctx_check_device(rst_ctx* c) {
     if (c->h_status[0] != kDevOk) {
         int code = c->h_status[0], where = c->h_status[1];
         RST_CUDA(c, cudaMemsetAsync(c->d_status, 0, 4 * sizeof(int), c->compute));
+        // a kernel that gave up may have left the election counter half-counted
+        RST_CUDA(c, cudaMemsetAsync(c->xent_counter, 0, 4 * sizeof(unsigned int), c->compute));
         return fail(c, RST_ERR_DEVICE_TIMEOUT,
                     "a kernel gave up a bounded wait (code %d, site %d); its output is invalid",
                     code, where);
