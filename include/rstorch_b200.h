@@ -208,6 +208,25 @@ int rst_stager_host(rst_stager* s, int slot, double** x_host, double** t_host);
 int rst_stager_submit(rst_stager* s, int slot);
 int rst_stager_acquire(rst_stager* s, int slot, rst_tensor** X, rst_tensor** T);
 
+/* ---- device-resident dataset and fused batch transform ------------------------
+ * The u8 samples and labels of a dataset (the reference's MNIST item type,
+ * src/data/dataset/hub/mnist.rs:181-194) are placed in HBM once.
+ * rst_dataset_gather builds the batch of the given sample indices in one kernel:
+ * per sample `flatten(normalize_zero_one(x))` (src/utils.rs:5-18, 30-35: min-max
+ * to [0,1] by the sample's own min and max, 0/0 = NaN for a constant sample) into
+ * row b of X (batch, features), and `one_hot(y, classes)` (src/utils.rs:38-42)
+ * into row b of T (batch, classes) -- the transform of README.md:44 applied by
+ * `ArrayDataLoaderIter::next` (src/data/data_loader.rs:192-207).  `indices` is a
+ * host array (sampler order, shuffled or not); an index outside the dataset is
+ * rejected, as is a label >= classes at creation (the reference panics on it). */
+typedef struct rst_dataset rst_dataset;
+int rst_dataset_create_u8(rst_ctx* ctx, const unsigned char* images, const unsigned char* labels,
+                          int64_t n, int64_t features, int64_t classes, rst_dataset** out);
+int rst_dataset_destroy(rst_dataset* d);
+int rst_dataset_len(const rst_dataset* d, int64_t* n);
+int rst_dataset_gather(rst_dataset* d, const int64_t* indices, int64_t batch, rst_tensor* X,
+                       rst_tensor* T);
+
 /* ---- data-parallel gradient exchange (no counterpart in the reference, which
  * is single-threaded; required to shard the batch over the GPUs of one box) --
  * One rank per process/GPU.  Rank 0 obtains an id, the caller ships the

@@ -80,6 +80,34 @@ def accuracy(pred, truth):
     return float((argmax(pred) == argmax(truth)).sum()) / float(pred.shape[0])
 
 
+def normalize_zero_one(x):
+    """src/utils.rs:5-18 for a u8 sample: max and min by `Ord` on the source type, then
+    `(R::from(v) - min) / (max - min)` in f64 (0/0 = NaN when the sample is constant)."""
+    mx, mn = float(x.max()), float(x.min())
+    with np.errstate(divide="ignore", invalid="ignore"):
+        return (x.astype(np.float64) - mn) / (mx - mn)
+
+
+def flatten(x):
+    """src/utils.rs:30-35: elements in logical (row-major) order."""
+    return np.ascontiguousarray(x).reshape(-1)
+
+
+def one_hot(label, n):
+    """src/utils.rs:38-42."""
+    out = np.zeros(n, dtype=np.float64)
+    out[int(label)] = 1.0
+    return out
+
+
+def iter_array_batch(images, labels, indices, classes):
+    """One batch of `ArrayDataLoaderIter::next` (src/data/data_loader.rs:192-207) over the
+    README transform `(flatten(normalize_zero_one(x)), one_hot(y, classes))` (README.md:44)."""
+    X = np.stack([flatten(normalize_zero_one(images[i])) for i in indices])
+    T = np.stack([one_hot(labels[i], classes) for i in indices])
+    return X, T
+
+
 def mlp_step(weights, X, T, lr, skip_first_dx=False):
     """One step in the order of src/model.rs:19-27 for Linear,ReLU,...,Linear.
     Returns (loss, acc, grads, new_weights, logits)."""

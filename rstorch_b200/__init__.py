@@ -14,7 +14,7 @@ its README loop) over a C-ABI library of sm_100a kernels:
 """
 from ._lib import RstError, exported_symbols
 from .core import Context, Graph, Tensor, Timer
-from .data import ArrayDataset, DataLoader, SequentialSampler
+from .data import ArrayDataset, DataLoader, DeviceDataset, SequentialSampler
 from .loss import CrossEntropyLoss, Loss
 from .module import (Identity, InitParameters, KaimingNormal, Linear, Module, Parameter, ReLU,
                      Sequential, sequential)
@@ -24,6 +24,7 @@ from .utils import accuracy, argmax, one_hot
 
 __all__ = [
     "RstError", "exported_symbols", "Context", "Graph", "Tensor", "Timer", "ArrayDataset", "DataLoader",
+    "DeviceDataset",
     "SequentialSampler", "CrossEntropyLoss", "Loss", "Identity", "InitParameters", "KaimingNormal",
     "Linear", "Module", "Parameter", "ReLU", "Sequential", "sequential", "SGD", "Optimizer",
     "Communicator", "backward_with_exchange", "shard_rows", "accuracy", "argmax", "one_hot",

@@ -82,6 +82,10 @@ _SIGNATURES = {
     "rst_stager_host": [P, C.c_int, C.POINTER(PD), C.POINTER(PD)],
     "rst_stager_submit": [P, C.c_int],
     "rst_stager_acquire": [P, C.c_int, PP, PP],
+    "rst_dataset_create_u8": [P, P, P, I64, I64, I64, PP],
+    "rst_dataset_destroy": [P],
+    "rst_dataset_len": [P, C.POINTER(I64)],
+    "rst_dataset_gather": [P, C.POINTER(I64), I64, P, P],
     "rst_comm_get_id": [P],
     "rst_comm_create": [P, P, C.c_int, C.c_int, PP],
     "rst_comm_destroy": [P],

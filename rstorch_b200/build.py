@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "librstorch_b200.so")
 SOURCES = ["runtime.cu", "ops.cu", "gemm_f64.cu", "xent.cu", "sgd.cu", "elementwise.cu",
-           "stager.cu", "comm.cu", "probe.cu", "synth.cu"]
+           "stager.cu", "comm.cu", "probe.cu", "synth.cu", "dataset.cu"]
 HEADERS = ["common.h", "mma_f64.cuh", os.path.join("..", "..", "include", "rstorch_b200.h")]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -1,0 +1,179 @@
+// Device-resident u8 dataset and the fused per-batch transform.
+//
+// The reference's training loop builds a batch on the CPU by calling, for each
+// of `batch_size` sampler indices, `dataset.get(index)` (one 28x28 u8 image and
+// its u8 label, src/data/dataset/hub/mnist.rs:181-194), the user transform
+// `(flatten(normalize_zero_one(x)), one_hot(y, 10))` (README.md:44;
+// src/utils.rs:5-18, 30-42) and `append` onto the batch arrays
+// (src/data/data_loader.rs:192-207).  Here the raw u8 samples live in HBM and one
+// kernel gathers the rows of a batch, normalises each sample to [0,1] with its own
+// min and max, and writes the f64 batch and the one-hot targets:
+//   x = (f64(v) - f64(min)) / (f64(max) - f64(min))      (utils.rs:13-17; 0/0 = NaN
+//                                                          for a constant sample)
+//   t = 1.0 at column `label`, 0.0 elsewhere              (utils.rs:38-42)
+// Per sample the kernel reads F bytes and writes 8*(F + classes) bytes.
+#include "common.h"
+
+using namespace rst;
+
+namespace {
+
+constexpr int kGatherThreads = 256;
+constexpr int kIndexSlots = 4;
+
+__global__ void __launch_bounds__(kGatherThreads)
+gather_normalize_onehot_kernel(const unsigned char* __restrict__ images, const unsigned char* __restrict__ labels,
+                               const long long* __restrict__ indices, long long batch, int features, int classes,
+                               double* __restrict__ X, double* __restrict__ T) {
+    const int lane = threadIdx.x & 31;
+    const long long warp_global = (long long)blockIdx.x * (kGatherThreads / 32) + (threadIdx.x >> 5);
+    const long long warp_stride = (long long)gridDim.x * (kGatherThreads / 32);
+    for (long long b = warp_global; b < batch; b += warp_stride) {
+        const long long idx = indices[b];
+        const unsigned char* src = images + idx * features;
+        // pass 1: min and max of the sample by the ordering of u8 (utils.rs:11-12)
+        unsigned int lo = 255u, hi = 0u;
+        for (int e = lane; e < features; e += 32) {
+            const unsigned int v = src[e];
+            lo = min(lo, v);
+            hi = max(hi, v);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+            hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+        }
+        const double dmin = (double)lo;
+        const double range = (double)hi - dmin;                     // max - min in f64 (utils.rs:14)
+        // pass 2: normalise; lanes write consecutive doubles
+        double* dst = X + b * features;
+        for (int e = lane; e < features; e += 32) dst[e] = ((double)src[e] - dmin) / range;
+        const int label = labels[idx];
+        double* trow = T + b * classes;
+        for (int c = lane; c < classes; c += 32) trow[c] = (c == label) ? 1.0 : 0.0;
+    }
+}
+
+}  // namespace
+
+struct rst_dataset {
+    rst_ctx* ctx;
+    long long n;
+    int features, classes;
+    unsigned char* d_images;
+    unsigned char* d_labels;
+    long long* h_idx[kIndexSlots];       // pinned
+    long long* d_idx[kIndexSlots];
+    cudaEvent_t idx_free[kIndexSlots];   // the gather that read the slot has finished
+    long long idx_cap;
+    int next_slot;
+    bool slot_used[kIndexSlots];
+};
+
+extern "C" int rst_dataset_destroy(rst_dataset* d);
+
+extern "C" int rst_dataset_create_u8(rst_ctx* c, const unsigned char* images, const unsigned char* labels,
+                                     int64_t n, int64_t features, int64_t classes, rst_dataset** out) {
+    if (!valid(c)) return fail(nullptr, RST_ERR_INVALID_ARG, "not a live context");
+    if (!out || !images || !labels || n <= 0 || features <= 0 || classes <= 0 || classes > 256 ||
+        features > 0x7fffffff)
+        return fail(c, RST_ERR_INVALID_ARG, "bad dataset arguments");
+    *out = nullptr;
+    if (c->capturing) return fail(c, RST_ERR_STATE, "dataset creation during graph capture");
+    // one_hot(label, classes) panics in the reference for label >= classes (utils.rs:40)
+    for (int64_t i = 0; i < n; ++i)
+        if (labels[i] >= classes)
+            return fail(c, RST_ERR_INVALID_ARG, "label %d of sample %lld is outside [0,%lld)", (int)labels[i],
+                        (long long)i, (long long)classes);
+    rst_dataset* d = new rst_dataset();
+    d->ctx = c; d->n = n; d->features = (int)features; d->classes = (int)classes;
+    d->d_images = nullptr; d->d_labels = nullptr; d->idx_cap = 0; d->next_slot = 0;
+    for (int s = 0; s < kIndexSlots; ++s) { d->h_idx[s] = nullptr; d->d_idx[s] = nullptr; d->idx_free[s] = nullptr; d->slot_used[s] = false; }
+    bool okay = cudaMalloc((void**)&d->d_images, (size_t)n * features) == cudaSuccess &&
+                cudaMalloc((void**)&d->d_labels, (size_t)n) == cudaSuccess &&
+                cudaMemcpy(d->d_images, images, (size_t)n * features, cudaMemcpyHostToDevice) == cudaSuccess &&
+                cudaMemcpy(d->d_labels, labels, (size_t)n, cudaMemcpyHostToDevice) == cudaSuccess;
+    for (int s = 0; okay && s < kIndexSlots; ++s)
+        okay = cudaEventCreateWithFlags(&d->idx_free[s], cudaEventDisableTiming) == cudaSuccess;
+    if (!okay) {
+        cudaGetLastError();
+        rst_dataset_destroy(d);
+        return fail(c, RST_ERR_OOM, "cannot place the dataset (%lld x %lld bytes) on the device", (long long)n,
+                    (long long)features);
+    }
+    *out = d;
+    return RST_OK;
+}
+
+extern "C" int rst_dataset_destroy(rst_dataset* d) {
+    if (!d) return RST_OK;
+    if (valid(d->ctx)) cudaStreamSynchronize(d->ctx->compute);
+    if (d->d_images) cudaFree(d->d_images);
+    if (d->d_labels) cudaFree(d->d_labels);
+    for (int s = 0; s < kIndexSlots; ++s) {
+        if (d->h_idx[s]) cudaFreeHost(d->h_idx[s]);
+        if (d->d_idx[s]) cudaFree(d->d_idx[s]);
+        if (d->idx_free[s]) cudaEventDestroy(d->idx_free[s]);
+    }
+    cudaGetLastError();
+    delete d;
+    return RST_OK;
+}
+
+extern "C" int rst_dataset_len(const rst_dataset* d, int64_t* n) {
+    if (!d || !n) return fail(nullptr, RST_ERR_INVALID_ARG, "bad argument");
+    *n = d->n;
+    return RST_OK;
+}
+
+extern "C" int rst_dataset_gather(rst_dataset* d, const int64_t* indices, int64_t batch, rst_tensor* X,
+                                  rst_tensor* T) {
+    if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
+    rst_ctx* c = d->ctx;
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, T, "T"));
+    if (batch <= 0 || !indices) return fail(c, RST_ERR_INVALID_ARG, "empty batch");
+    if (X->rows != batch || X->cols != d->features || T->rows != batch || T->cols != d->classes)
+        return fail(c, RST_ERR_SHAPE, "gather of %lld samples into X (%lld,%lld), T (%lld,%lld); dataset has %d features, %d classes",
+                    (long long)batch, (long long)X->rows, (long long)X->cols, (long long)T->rows, (long long)T->cols,
+                    d->features, d->classes);
+    if (c->capturing) return fail(c, RST_ERR_STATE, "gather during graph capture");
+    // `dataset.get(index)?` ends the reference's epoch on a missing sample (data_loader.rs:197)
+    for (int64_t i = 0; i < batch; ++i)
+        if (indices[i] < 0 || indices[i] >= d->n)
+            return fail(c, RST_ERR_INVALID_ARG, "index %lld outside the dataset of %lld samples", (long long)indices[i],
+                        (long long)d->n);
+    if (batch > d->idx_cap) {
+        RST_CUDA(c, cudaStreamSynchronize(c->compute));
+        for (int s = 0; s < kIndexSlots; ++s) {
+            if (d->h_idx[s]) cudaFreeHost(d->h_idx[s]);
+            if (d->d_idx[s]) cudaFree(d->d_idx[s]);
+            d->h_idx[s] = nullptr; d->d_idx[s] = nullptr; d->slot_used[s] = false;
+            if (cudaMallocHost((void**)&d->h_idx[s], (size_t)batch * sizeof(long long)) != cudaSuccess ||
+                cudaMalloc((void**)&d->d_idx[s], (size_t)batch * sizeof(long long)) != cudaSuccess) {
+                cudaGetLastError();
+                d->idx_cap = 0;
+                return fail(c, RST_ERR_OOM, "cannot allocate index staging for %lld samples", (long long)batch);
+            }
+        }
+        d->idx_cap = batch;
+    }
+    const int s = d->next_slot;
+    d->next_slot = (s + 1) % kIndexSlots;
+    if (d->slot_used[s]) RST_CUDA(c, cudaEventSynchronize(d->idx_free[s]));   // its previous gather has run
+    for (int64_t i = 0; i < batch; ++i) d->h_idx[s][i] = indices[i];
+    RST_CUDA(c, cudaMemcpyAsync(d->d_idx[s], d->h_idx[s], (size_t)batch * sizeof(long long), cudaMemcpyHostToDevice,
+                                c->compute));
+    {
+        ProfScope prof(c, "gather");
+        long long blocks = (batch + kGatherThreads / 32 - 1) / (kGatherThreads / 32);
+        long long cap = (long long)c->num_sms * 8;
+        if (blocks > cap) blocks = cap;
+        gather_normalize_onehot_kernel<<<(int)blocks, kGatherThreads, 0, c->compute>>>(
+            d->d_images, d->d_labels, d->d_idx[s], batch, d->features, d->classes, X->data, T->data);
+        RST_TRY(after_launch(c, "gather_normalize_onehot_kernel"));
+    }
+    RST_CUDA(c, cudaEventRecord(d->idx_free[s], c->compute));
+    d->slot_used[s] = true;
+    return RST_OK;
+}

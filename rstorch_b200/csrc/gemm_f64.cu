@@ -413,15 +413,15 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
     const long long k_tiles = (a.K + kBK - 1) / kBK;
     const long long tiles_large = ((a.M + 127) / 128) * ((a.N + 127) / 128);
     if (tiles_large >= ctx->num_sms) return launch_cfg<128, 128, 2, 4, 6, A_K, B_K, false>(ctx, a, p, 1);
-    // Small problems: 64x64 tiles, and split K until the grid covers the GPU about
-    // twice, keeping at least four k-tiles per split and at most 16 splits.
+    // Small problems: 64x64 tiles.  CTAs that share an SM share its f64 tensor pipe,
+    // so more than one wave of CTAs buys nothing: split K only as far as the grid
+    // still fits one wave, keeping at least four k-tiles per split and at most 16
+    // splits (the reduce kernel reads every partial).
     const long long tiles_small = ((a.M + 63) / 64) * ((a.N + 63) / 64);
-    long long splits = 1;
-    if (tiles_small < 2LL * ctx->num_sms) {
-        splits = (2LL * ctx->num_sms + tiles_small - 1) / tiles_small;
-        splits = std::min(splits, std::max(1LL, k_tiles / 4));
-        splits = std::min(splits, 16LL);
-    }
+    long long splits = ctx->num_sms / tiles_small;
+    splits = std::min(splits, k_tiles / 4);
+    splits = std::min(splits, 16LL);
+    splits = std::max(splits, 1LL);
     constexpr bool kFuse = !A_K && !B_K;     // the dW product also yields db
     if (kFuse && a.colsum_out && colsum_done) *colsum_done = true;
     return launch_cfg<64, 64, 2, 2, 4, A_K, B_K, kFuse>(ctx, a, p, (int)splits);

@@ -29,6 +29,45 @@ class ArrayDataset:
         return len(self.samples)
 
 
+class DeviceDataset:
+    """u8 samples and labels resident in HBM (the item type of the reference's MNIST
+    dataset, src/data/dataset/hub/mnist.rs:181-194) with the README transform
+    `(flatten(normalize_zero_one(x)), one_hot(y, classes))` (README.md:44) applied by
+    the gather kernel when a batch is built."""
+
+    def __init__(self, ctx: Context, images: np.ndarray, labels: np.ndarray, classes: int):
+        images = np.ascontiguousarray(images, dtype=np.uint8)
+        labels = np.ascontiguousarray(labels, dtype=np.uint8).reshape(-1)
+        if len(images) != len(labels):
+            raise ValueError("images and labels differ in length")
+        self.ctx, self.n, self.classes = ctx, len(labels), int(classes)
+        self.features = int(np.prod(images.shape[1:])) if images.ndim > 1 else 1
+        h = C.c_void_p()
+        ctx._check(ctx._lib.rst_dataset_create_u8(ctx.handle, images.ctypes.data_as(C.c_void_p),
+                                                  labels.ctypes.data_as(C.c_void_p), self.n, self.features,
+                                                  self.classes, C.byref(h)))
+        self.handle = h
+
+    def __len__(self) -> int:
+        return self.n
+
+    def gather(self, indices: np.ndarray, X: Tensor, T: Tensor) -> None:
+        idx = np.ascontiguousarray(indices, dtype=np.int64)
+        self.ctx._check(self.ctx._lib.rst_dataset_gather(self.handle, idx.ctypes.data_as(C.POINTER(C.c_int64)),
+                                                         len(idx), X.handle, T.handle))
+
+    def close(self) -> None:
+        if self.handle is not None and self.handle.value and self.ctx.handle.value:
+            self.ctx._lib.rst_dataset_destroy(self.handle)
+        self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class SequentialSampler:
     """0..size (src/data/sampler.rs:31-43)."""
 
@@ -96,12 +135,27 @@ class DataLoader:
         return (Tensor(ctx, hx, b, self.dataset.samples.shape[1], owns=False),
                 Tensor(ctx, ht, b, self.dataset.targets.shape[1], owns=False))
 
+    def _iter_device(self, order: np.ndarray) -> Iterator[tuple[Tensor, Tensor]]:
+        """Batches of a DeviceDataset: the gather kernel writes into a small ring of
+        output tensors (a batch stays valid until `slots` later batches were asked for)."""
+        ds, b = self.dataset, self.batch_size
+        ring = max(2, self._slots)
+        if getattr(self, "_out_ring", None) is None or len(self._out_ring) != ring:
+            self._out_ring = [(self.ctx.empty(b, ds.features), self.ctx.empty(b, ds.classes)) for _ in range(ring)]
+        for k in range(len(order) // b):
+            X, T = self._out_ring[k % ring]
+            ds.gather(order[k * b:(k + 1) * b], X, T)
+            yield X, T
+
     def iter_array(self) -> Iterator[tuple[Tensor, Tensor]]:
-        self._ensure_stager()
         order = np.fromiter(self.sampler.iter(), dtype=np.int64)
         if self._shuffle:
             perm = self._rng.permutation(len(self.dataset))
             order = perm[order]
+        if isinstance(self.dataset, DeviceDataset):
+            yield from self._iter_device(order[order < len(self.dataset)])
+            return
+        self._ensure_stager()
         order = order[order < len(self.dataset)] if (order >= len(self.dataset)).any() else order
         n_batches = len(order) // self.batch_size
         b = self.batch_size

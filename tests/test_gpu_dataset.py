@@ -1,0 +1,95 @@
+"""Device-resident dataset + fused gather/normalise/flatten/one-hot kernel against the
+numpy restatement of the README transform and of `iter_array` (bit-exact: u8 -> f64
+conversion, one subtraction and one correctly rounded division per element)."""
+import numpy as np
+import pytest
+
+import rstorch_b200 as rt
+from oracle import oracle_np as on
+from rstorch_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def test_gather_matches_the_readme_transform(ctx):
+    images, labels = synth.mnist_like_u8(0, 0, 300)
+    images[7] = 0                 # constant samples: (v - min) / 0 = NaN in the reference
+    images[8] = 200
+    images[9, 0, 0], images[9, 27, 27] = 3, 250          # min and max away from 0 and 255
+    ds = rt.DeviceDataset(ctx, images, labels, 10)
+    assert len(ds) == 300 and ds.features == 784
+    rng = np.random.default_rng(0)
+    for idx in (np.arange(32), np.array([9, 8, 7, 299, 0, 7]), rng.permutation(300)[:256]):
+        X, T = ctx.empty(len(idx), 784), ctx.empty(len(idx), 10)
+        ds.gather(idx, X, T)
+        want_x, want_t = on.iter_array_batch(images, labels, idx, 10)
+        assert np.array_equal(X.numpy(), want_x, equal_nan=True)
+        assert np.array_equal(T.numpy(), want_t)
+    assert np.isnan(want_x[:, 0]).sum() >= 1
+    ds.close()
+
+
+def test_data_loader_over_a_device_dataset(ctx):
+    images, labels = synth.mnist_like_u8(1, 0, 100, side=4, classes=7)
+    ds = rt.DeviceDataset(ctx, images, labels, 7)
+    dl = rt.DataLoader(ds, 32, False, rt.SequentialSampler(len(ds)), ctx)
+    assert len(dl) == 3
+    got = [(x.numpy(), t.numpy()) for x, t in dl.iter_array()]
+    assert len(got) == 3                                 # the 4 left-over samples are dropped
+    for k, (x, t) in enumerate(got):
+        want_x, want_t = on.iter_array_batch(images, labels, np.arange(k * 32, k * 32 + 32), 7)
+        assert np.array_equal(x, want_x, equal_nan=True) and np.array_equal(t, want_t)
+    # seeded shuffle: every epoch is a new permutation, every sample at most once per epoch
+    dl2 = rt.DataLoader(ds, 25, True, rt.SequentialSampler(len(ds)), ctx, shuffle_seed=3)
+    e1 = np.concatenate([t.numpy().argmax(axis=1) for _, t in dl2.iter_array()])
+    e2 = np.concatenate([t.numpy().argmax(axis=1) for _, t in dl2.iter_array()])
+    assert len(e1) == 100 and sorted(e1) == sorted(labels.tolist()) and not np.array_equal(e1, e2)
+
+
+def test_training_from_the_device_dataset_matches_the_host_path(ctx):
+    """Same samples through both loaders give the same training trajectory."""
+    images, labels = synth.mnist_like_u8(2, 0, 128)
+    X, T = on.iter_array_batch(images, labels, np.arange(128), 10)
+
+    def run(loader):
+        layers = []
+        for l, (w, b) in enumerate(synth.mlp_weights(0, [784, 32, 10])):
+            class Init(rt.InitParameters):
+                def weight(self, i, o, w=w):
+                    return w
+
+                def bias(self, i, o, b=b):
+                    return b
+            layers.append(rt.Linear.new_with_kernel(w.shape[1], w.shape[0], Init(), ctx))
+            if l == 0:
+                layers.append(rt.ReLU())
+        model, loss_fn, opt = rt.sequential(*layers), rt.CrossEntropyLoss(), rt.SGD.new(0.1)
+        losses = []
+        for x, t in loader.iter_array():
+            losses.append(loss_fn.forward(model.forward(x), t))
+            model.backward(loss_fn.backward(), need_input_grad=False)
+            opt.step(model)
+        return losses, [p.parm.numpy() for p in model.parameters()]
+
+    dev = rt.DataLoader(rt.DeviceDataset(ctx, images, labels, 10), 32, False, rt.SequentialSampler(128), ctx)
+    host = rt.DataLoader(rt.ArrayDataset(X, T), 32, False, rt.SequentialSampler(128), ctx)
+    l1, p1 = run(dev)
+    l2, p2 = run(host)
+    assert l1 == l2 and len(l1) == 4
+    for a, b in zip(p1, p2):
+        assert np.array_equal(a, b)
+
+
+def test_dataset_errors(ctx):
+    images, labels = synth.mnist_like_u8(0, 0, 10, side=2)
+    with pytest.raises(rt.RstError) as e:
+        rt.DeviceDataset(ctx, images, labels, 5)          # labels reach 9: one_hot(9, 5) panics in the reference
+    assert e.value.status == _lib.RST_ERR_INVALID_ARG
+    ds = rt.DeviceDataset(ctx, images, labels, 10)
+    X, T = ctx.empty(2, 4), ctx.empty(2, 10)
+    with pytest.raises(rt.RstError) as e:
+        ds.gather(np.array([0, 10]), X, T)                # index 10 is outside the 10 samples
+    assert e.value.status == _lib.RST_ERR_INVALID_ARG
+    with pytest.raises(rt.RstError) as e:
+        ds.gather(np.array([0, 1, 2]), X, T)
+    assert e.value.status == _lib.RST_ERR_SHAPE

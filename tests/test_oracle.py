@@ -114,6 +114,22 @@ def test_argmax_first_maximum_wins(oc):
     assert oc.accuracy(x, t) == pytest.approx(4 / 5)
 
 
+def test_readme_transform_restatement():
+    x = np.array([[10, 60], [110, 210]], dtype=np.uint8)
+    assert on.flatten(on.normalize_zero_one(x)).tolist() == [0.0, 0.25, 0.5, 1.0]
+    assert np.isnan(on.normalize_zero_one(np.full((2, 2), 7, dtype=np.uint8))).all()     # 0 / 0
+    assert on.one_hot(2, 4).tolist() == [0.0, 0.0, 1.0, 0.0]
+    with pytest.raises(IndexError):
+        on.one_hot(4, 4)
+    from rstorch_b200 import synth
+    images, labels = synth.mnist_like_u8(0, 0, 64)
+    assert images.shape == (64, 28, 28) and images.dtype == np.uint8 and labels.max() < 10
+    assert 0.78 < (images == 0).mean() < 0.84
+    X, T = on.iter_array_batch(images, labels, [5, 3], 10)
+    assert X.shape == (2, 784) and T.shape == (2, 10) and X.max() == 1.0 and X.min() == 0.0
+    assert T[0].argmax() == labels[5] and T.sum() == 2.0
+
+
 # ---- committed golden steps ------------------------------------------------------------
 def test_golden_steps_cpp(oc, golden_steps):
     g = golden_steps
