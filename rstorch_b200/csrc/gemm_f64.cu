@@ -176,73 +176,82 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t a_box_off = (uint32_t)(wm * C_::WTM / 16) * kBoxBytes;         // + mt*2048
     const uint32_t b_box_off = (uint32_t)(wn * C_::WTN / 16) * kBoxBytes;         // + (nt/2)*2048
 
-    bool ok = true;
-    int it = 0;
-    for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        if (!mbar_wait_bounded(full_bar(s), ph)) {
-            atomicExch(p.status, kDevBarrierTimeout);
-            atomicExch(p.status + 1, 2);
-            ok = false;     // results are invalid; keep going so that barriers and counters stay consistent
-            break;
+    // Fragments of k sub-step i (0 or 1) of the stage at (As, Bs).
+    auto load_frags = [&](uint32_t As, uint32_t Bs, int i, double (&a)[MT][4], double (&b)[NT][2]) {
+        // rows of an M-/N-major tile that feed logical k = t and k = t+4 of this sub-step
+        const int kr0 = C_::kMnNatural ? (8 * i + 2 * t) : (4 * t + 2 * i);
+        const int kr1 = kr0 + 1;
+        const uint32_t mn_off0 = (uint32_t)kr0 * kRowBytes + ((uint32_t)(g ^ (kr0 & 7)) << 4);
+        const uint32_t mn_off1 = (uint32_t)kr1 * kRowBytes + ((uint32_t)(g ^ (kr1 & 7)) << 4);
+        const uint32_t kchunk = kchunk0 ^ ((uint32_t)i << 4);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            if (A_K) {
+                const uint32_t addr = As + a_row_off + (uint32_t)mt * 16 * kRowBytes + kchunk;
+                lds128(a[mt][0], a[mt][2], addr);                 // row g   : k = t, t+4
+                lds128(a[mt][1], a[mt][3], addr + 8 * kRowBytes); // row g+8
+            } else {
+                const uint32_t box = As + a_box_off + (uint32_t)mt * kBoxBytes;
+                lds128(a[mt][0], a[mt][1], box + mn_off0);        // k = t   : m = 2g, 2g+1
+                lds128(a[mt][2], a[mt][3], box + mn_off1);        // k = t+4
+            }
         }
-        const uint32_t As = smem_base + (uint32_t)s * C_::kStageBytes;
-        const uint32_t Bs = As + C_::kABytes;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            // rows of an M-/N-major tile that feed logical k = t and k = t+4 of this sub-step
-            const int kr0 = C_::kMnNatural ? (8 * i + 2 * t) : (4 * t + 2 * i);
-            const int kr1 = kr0 + 1;
-            const uint32_t mn_off0 = (uint32_t)kr0 * kRowBytes + ((uint32_t)(g ^ (kr0 & 7)) << 4);
-            const uint32_t mn_off1 = (uint32_t)kr1 * kRowBytes + ((uint32_t)(g ^ (kr1 & 7)) << 4);
-            const uint32_t kchunk = kchunk0 ^ ((uint32_t)i << 4);
-
-            double a[MT][4], b[NT][2];
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                if (A_K) {
-                    const uint32_t addr = As + a_row_off + (uint32_t)mt * 16 * kRowBytes + kchunk;
-                    lds128(a[mt][0], a[mt][2], addr);                 // row g   : k = t, t+4
-                    lds128(a[mt][1], a[mt][3], addr + 8 * kRowBytes); // row g+8
-                } else {
-                    const uint32_t box = As + a_box_off + (uint32_t)mt * kBoxBytes;
-                    lds128(a[mt][0], a[mt][1], box + mn_off0);        // k = t   : m = 2g, 2g+1
-                    lds128(a[mt][2], a[mt][3], box + mn_off1);        // k = t+4
-                }
+        for (int nt = 0; nt < NT; ++nt) {
+            if (B_K) {
+                const uint32_t addr = Bs + b_row_off + (uint32_t)nt * 8 * kRowBytes + kchunk;
+                lds128(b[nt][0], b[nt][1], addr);                 // n = g : k = t, t+4
+            } else if ((nt & 1) == 0) {
+                const uint32_t box = Bs + b_box_off + (uint32_t)(nt / 2) * kBoxBytes;
+                lds128(b[nt][0], b[nt + 1][0], box + mn_off0);    // k = t   : n = 2g (even tile), 2g+1 (odd tile)
+                lds128(b[nt][1], b[nt + 1][1], box + mn_off1);    // k = t+4
             }
-            if (FUSE_COLSUM) {
-                if (do_colsum) {
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        asum[mt][0] += a[mt][0] + a[mt][2];           // m = 2g
-                        asum[mt][1] += a[mt][1] + a[mt][3];           // m = 2g+1
-                    }
-                }
-            }
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                if (B_K) {
-                    const uint32_t addr = Bs + b_row_off + (uint32_t)nt * 8 * kRowBytes + kchunk;
-                    lds128(b[nt][0], b[nt][1], addr);                 // n = g : k = t, t+4
-                } else if ((nt & 1) == 0) {
-                    const uint32_t box = Bs + b_box_off + (uint32_t)(nt / 2) * kBoxBytes;
-                    lds128(b[nt][0], b[nt + 1][0], box + mn_off0);    // k = t   : n = 2g (even tile), 2g+1 (odd tile)
-                    lds128(b[nt][1], b[nt + 1][1], box + mn_off1);    // k = t+4
-                }
-            }
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) dmma_m16n8k8(acc[mt][nt], a[mt], b[nt]);
         }
-        // The stage is about to be rewritten by TMA (async proxy) after having been
-        // read with ordinary shared loads (generic proxy): every reader orders its
-        // reads against the async proxy before the warp releases the stage.  Without
-        // this fence, refilled stages were observed half-written on B200.
+    };
+    auto multiply = [&](const double (&a)[MT][4], const double (&b)[NT][2]) {
+        if (FUSE_COLSUM) {
+            if (do_colsum) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    asum[mt][0] += a[mt][0] + a[mt][2];           // m = 2g
+                    asum[mt][1] += a[mt][1] + a[mt][3];           // m = 2g+1
+                }
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) dmma_m16n8k8(acc[mt][nt], a[mt], b[nt]);
+    };
+    auto wait_full = [&](int it) -> bool {
+        if (mbar_wait_bounded(full_bar(it % STAGES), (uint32_t)(it / STAGES) & 1u)) return true;
+        atomicExch(p.status, kDevBarrierTimeout);
+        atomicExch(p.status + 1, 2);
+        return false;       // results are invalid from here on
+    };
+    // The stage is about to be rewritten by TMA (async proxy) after having been read
+    // with ordinary shared loads (generic proxy): every reader orders its reads against
+    // the async proxy before the warp releases the stage.  Without this fence, refilled
+    // stages were observed half-written on B200.
+    auto release = [&](int it) {
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(empty_bar(s));
+        if (lane == 0) mbar_arrive(empty_bar(it % STAGES));
+    };
+    auto stage_a = [&](int it) { return smem_base + (uint32_t)(it % STAGES) * C_::kStageBytes; };
+
+    bool ok = true;
+    const int n_it = kt_end - kt_begin;
+    for (int it = 0; it < n_it; ++it) {
+        if (!wait_full(it)) { ok = false; break; }
+        const uint32_t As = stage_a(it);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            double a[MT][4], b[NT][2];
+            load_frags(As, As + C_::kABytes, i, a, b);
+            multiply(a, b);
+        }
+        release(it);
     }
 
     // ---------------- epilogue: registers -> global ----------------
@@ -408,6 +417,13 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     return RST_OK;
 }
 
+// Tile configuration for problems with fewer than one wave of 128x128 tiles: 64x64
+// tiles, 8 consumer warps (two per SM sub-partition, so that one warp's shared loads
+// and barrier traffic hide behind the other's MMAs), 8 stages of 16 KiB (one CTA per
+// SM has to keep enough bytes in flight to cover the latency of operands that are not
+// in L2 yet; a TMA tile load takes about 1.5 us even from L2).
+constexpr int kSmallBM = 64, kSmallBN = 64, kSmallWM = 2, kSmallWN = 4, kSmallStages = 8;
+
 template <bool A_K, bool B_K>
 int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_done) {
     const long long k_tiles = (a.K + kBK - 1) / kBK;
@@ -417,14 +433,14 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
     // so more than one wave of CTAs buys nothing: split K only as far as the grid
     // still fits one wave, keeping at least four k-tiles per split and at most 16
     // splits (the reduce kernel reads every partial).
-    const long long tiles_small = ((a.M + 63) / 64) * ((a.N + 63) / 64);
+    const long long tiles_small = ((a.M + kSmallBM - 1) / kSmallBM) * ((a.N + kSmallBN - 1) / kSmallBN);
     long long splits = ctx->num_sms / tiles_small;
     splits = std::min(splits, k_tiles / 4);
     splits = std::min(splits, 16LL);
     splits = std::max(splits, 1LL);
     constexpr bool kFuse = !A_K && !B_K;     // the dW product also yields db
     if (kFuse && a.colsum_out && colsum_done) *colsum_done = true;
-    return launch_cfg<64, 64, 2, 2, 4, A_K, B_K, kFuse>(ctx, a, p, (int)splits);
+    return launch_cfg<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, A_K, B_K, kFuse>(ctx, a, p, (int)splits);
 }
 
 }  // namespace
