@@ -258,6 +258,8 @@ def mlp_arm(args) -> None:
     rank, world, local, dist = init_distributed(args.gpus)
     wl = args.workload
     dims, global_batch, stream, identity = WORKLOADS[wl]
+    if args.batch:
+        global_batch = args.batch
     first_row, rows = rt.shard_rows(global_batch, rank, world)
     ctx = rt.Context(local)
     comm = rt.Communicator.from_torch_distributed(ctx) if dist is not None else None
@@ -543,6 +545,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOAD_NAMES), default="c4")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the workload's global batch (profiler captures and parity runs; "
+                         "the benchmark numbers use the workload's own batch)")
     ap.add_argument("--sgd-log2-params", type=int, default=30,
                     help="workload c5 only: log2 of the parameter count (30 is the benchmark size; "
                          "smaller values are for profiler captures)")

@@ -96,6 +96,15 @@ __device__ __forceinline__ int row_argmax(const double (&v)[EPL], int lane, int 
     return first_is_nan ? 0 : best.i;
 }
 
+// t * ln(p), the summand of cross_entropy.rs:38.  The f64 logarithm is the most
+// expensive part of the kernel and, with one-hot targets, all but one term per row are
+// 0 * ln(p) with p > 0, i.e. a signed zero that leaves the sum unchanged; those skip the
+// logarithm.  p == 0 (0 * -inf = NaN), NaN and non-zero targets take the full expression,
+// so the value of the loss is the reference's in every case.
+__device__ __forceinline__ double loss_term(double t, double p) {
+    return (t == 0.0 && p > 0.0) ? 0.0 : t * log(p);
+}
+
 struct BlockPartial {
     double loss;      // Σ t · ln p over the block's rows
     double correct;
@@ -214,7 +223,7 @@ xent_rows_kernel(const double* __restrict__ logits, const double* __restrict__ t
             if (live && col < cols) {
                 double p = x[j] / s;
                 if (MODE == 0) {
-                    row_loss += t[j] * log(p);
+                    row_loss += loss_term(t[j], p);
                     if (out) out[row * cols + col] = p - t[j];
                 } else {
                     out[row * cols + col] = p;
@@ -278,7 +287,7 @@ xent_wide_kernel(const double* __restrict__ logits, const double* __restrict__ t
             double p = exp(xr[col] - m) / s;
             if (MODE == 0) {
                 double t = tr[col];
-                row_loss += t * log(p);
+                row_loss += loss_term(t, p);
                 if (out) out[row * cols + col] = p - t;
             } else {
                 out[row * cols + col] = p;
