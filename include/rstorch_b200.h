@@ -158,6 +158,16 @@ int rst_relu_backward(rst_ctx* ctx, const rst_tensor* dY, const rst_tensor* X_pr
 /* ---- softmax free function (src/module/activation/softmax.rs:36-53) ------ */
 int rst_softmax(rst_ctx* ctx, const rst_tensor* X, rst_tensor* P);
 
+/* ---- Softmax module (src/module/activation/softmax.rs:5-34, 55-78) ---------
+ * Forward over axis 1 is rst_softmax; rst_softmax_axis0 normalises every column
+ * (Softmax::with_axis(0)).  rst_softmax_backward reproduces the reference's
+ * backward as written: jacobian = -(outputᵀ·output) taken over the whole batch,
+ * diagonal replaced by s(1-s) with s = Σ_b output[b][j]² (softmax.rs:66-70),
+ * dX = gradient · jacobian (softmax.rs:72).  `output` is what forward returned. */
+int rst_softmax_axis0(rst_ctx* ctx, const rst_tensor* X, rst_tensor* P);
+int rst_softmax_backward(rst_ctx* ctx, const rst_tensor* output, const rst_tensor* gradient,
+                         rst_tensor* dX);
+
 /* ---- CrossEntropyLoss (src/loss/cross_entropy.rs:32-48) + accuracy --------
  * One pass over the rows computes
  *   p = softmax(logits, axis 1)                      (cross_entropy.rs:37)

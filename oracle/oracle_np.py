@@ -45,6 +45,22 @@ def softmax(x):
     return e / e.sum(axis=1, keepdims=True)
 
 
+def softmax_axis(x, axis):
+    """src/module/activation/softmax.rs:45-53 for either axis."""
+    m = np.maximum(np.max(np.where(np.isnan(x), F64_MIN, x), axis=axis, keepdims=True), F64_MIN)
+    e = np.exp(x - m)
+    return e / e.sum(axis=axis, keepdims=True)
+
+
+def softmax_module_backward(output, gradient):
+    """Softmax::backward, src/module/activation/softmax.rs:62-75: jacobian = -(outputᵀ·output);
+    each diagonal element el becomes -el and then el·(1 - el); result = gradient · jacobian."""
+    jac = -(output.T @ output)
+    d = -np.diag(jac)
+    jac[np.diag_indices_from(jac)] = d * (1.0 - d)
+    return gradient @ jac
+
+
 def xent_forward(pred, truth):
     """src/loss/cross_entropy.rs:34-42 -> (loss, cached softmax)."""
     p = softmax(pred)

@@ -16,8 +16,8 @@ from ._lib import RstError, exported_symbols
 from .core import Context, Graph, Tensor, Timer
 from .data import ArrayDataset, DataLoader, DeviceDataset, SequentialSampler
 from .loss import CrossEntropyLoss, Loss
-from .module import (Identity, InitParameters, KaimingNormal, Linear, Module, Parameter, ReLU,
-                     Sequential, sequential)
+from .module import (Identity, InitParameters, KaimingNormal, Linear, Module, Normal, Parameter, ReLU,
+                     Sequential, Softmax, XavierNormal, sequential)
 from .optim import SGD, Optimizer
 from .parallel import Communicator, backward_with_exchange, shard_rows
 from .utils import accuracy, argmax, one_hot
@@ -26,6 +26,7 @@ __all__ = [
     "RstError", "exported_symbols", "Context", "Graph", "Tensor", "Timer", "ArrayDataset", "DataLoader",
     "DeviceDataset",
     "SequentialSampler", "CrossEntropyLoss", "Loss", "Identity", "InitParameters", "KaimingNormal",
-    "Linear", "Module", "Parameter", "ReLU", "Sequential", "sequential", "SGD", "Optimizer",
+    "Linear", "Module", "Normal", "Parameter", "ReLU", "Sequential", "Softmax", "XavierNormal", "sequential",
+    "SGD", "Optimizer",
     "Communicator", "backward_with_exchange", "shard_rows", "accuracy", "argmax", "one_hot",
 ]

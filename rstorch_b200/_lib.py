@@ -68,6 +68,8 @@ _SIGNATURES = {
     "rst_relu_forward": [P, P, P],
     "rst_relu_backward": [P, P, P, P],
     "rst_softmax": [P, P, P],
+    "rst_softmax_axis0": [P, P, P],
+    "rst_softmax_backward": [P, P, P, P],
     "rst_xent_slots": [],
     "rst_xent_forward_backward": [P, P, P, P, C.c_int],
     "rst_xent_result": [P, C.c_int, PD, PD],

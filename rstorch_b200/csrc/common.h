@@ -162,6 +162,8 @@ int launch_relu_forward(rst_ctx* ctx, const double* x, double* y, int64_t n);
 int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, double* dx,
                          int64_t n);
 int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n);
+int launch_softmax_axis0(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols);
+int launch_softmax_jacobian_diag(rst_ctx* ctx, double* J, int64_t n);
 int launch_softmax(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols);
 int launch_xent(rst_ctx* ctx, const double* logits, const double* truth, double* dlogits,
                 int64_t rows, int64_t cols, ResultSlot* d_slot);

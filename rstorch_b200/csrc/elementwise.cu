@@ -56,6 +56,35 @@ __global__ void __launch_bounds__(kThreads) relu_backward_kernel(const double* _
     }
 }
 
+// Softmax over axis 0 (every column sums to one; Softmax::with_axis(0),
+// src/module/activation/softmax.rs:21-27,45-53).  One thread per column, so a warp
+// reads consecutive elements of a row; the maximum is folded from f64::MIN.
+__global__ void __launch_bounds__(kThreads) softmax_axis0_kernel(const double* __restrict__ x,
+                                                                 double* __restrict__ p, int64_t rows,
+                                                                 int64_t cols) {
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    double m = -1.7976931348623157e308;
+    for (int64_t r = 0; r < rows; ++r) {
+        const double v = x[r * cols + c];
+        m = v > m ? v : m;
+    }
+    double s = 0.0;
+    for (int64_t r = 0; r < rows; ++r) s += exp(x[r * cols + c] - m);
+    for (int64_t r = 0; r < rows; ++r) p[r * cols + c] = exp(x[r * cols + c] - m) / s;
+}
+
+// Diagonal of the Softmax module's Jacobian: J holds -OᵀO; each diagonal element becomes
+// s(1 - s) with s = -J[j][j]                        (src/module/activation/softmax.rs:67-70)
+__global__ void __launch_bounds__(kThreads) softmax_jacobian_diag_kernel(double* __restrict__ J, int64_t n) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    double el = J[j * n + j];
+    el = -el;
+    el = el * (1.0 - el);
+    J[j * n + j] = el;
+}
+
 __global__ void __launch_bounds__(kThreads) fill_kernel(double* __restrict__ x, double v, int64_t n) {
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -131,6 +160,18 @@ int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, dou
     int vec = aligned16(dy) && aligned16(xpre) && aligned16(dx);
     relu_backward_kernel<<<grid_for(ctx, vec ? n / 2 + 1 : n, 8), kThreads, 0, ctx->compute>>>(dy, xpre, dx, n, vec);
     return after_launch(ctx, "relu_backward_kernel");
+}
+
+int launch_softmax_axis0(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols) {
+    if (rows == 0 || cols == 0) return RST_OK;
+    softmax_axis0_kernel<<<(unsigned)((cols + kThreads - 1) / kThreads), kThreads, 0, ctx->compute>>>(x, p, rows, cols);
+    return after_launch(ctx, "softmax_axis0_kernel");
+}
+
+int launch_softmax_jacobian_diag(rst_ctx* ctx, double* J, int64_t n) {
+    if (n == 0) return RST_OK;
+    softmax_jacobian_diag_kernel<<<(unsigned)((n + kThreads - 1) / kThreads), kThreads, 0, ctx->compute>>>(J, n);
+    return after_launch(ctx, "softmax_jacobian_diag_kernel");
 }
 
 int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n) {

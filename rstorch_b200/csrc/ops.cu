@@ -143,6 +143,52 @@ extern "C" int rst_softmax(rst_ctx* c, const rst_tensor* X, rst_tensor* P) {
     return launch_softmax(c, X->data, P->data, X->rows, X->cols);
 }
 
+// Softmax module, forward over axis 0 (src/module/activation/softmax.rs:21-27,45-53).
+extern "C" int rst_softmax_axis0(rst_ctx* c, const rst_tensor* X, rst_tensor* P) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, P, "P"));
+    RST_TRY(same_shape(c, X, P, "softmax"));
+    return launch_softmax_axis0(c, X->data, P->data, X->rows, X->cols);
+}
+
+// Softmax::backward (src/module/activation/softmax.rs:62-75), kept exactly as the
+// reference computes it: jacobian = -(outputᵀ·output) over the whole batch, its diagonal
+// replaced by s(1-s) with s = Σ_b output[b][j]², result = gradient · jacobian.
+extern "C" int rst_softmax_backward(rst_ctx* c, const rst_tensor* output, const rst_tensor* gradient,
+                                    rst_tensor* dX) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, output, "output"));
+    RST_TRY(check_tensor(c, gradient, "gradient"));
+    RST_TRY(check_tensor(c, dX, "dX"));
+    const int64_t B = output->rows, C = output->cols;
+    if (gradient->cols != C)
+        return fail(c, RST_ERR_SHAPE, "Softmax::backward: gradient (%lld,%lld) against output (%lld,%lld)",
+                    (long long)gradient->rows, (long long)gradient->cols, (long long)B, (long long)C);
+    if (dX->rows != gradient->rows || dX->cols != C)
+        return fail(c, RST_ERR_SHAPE, "Softmax::backward: result must be (%lld,%lld)", (long long)gradient->rows,
+                    (long long)C);
+    rst_tensor* J = nullptr;
+    RST_TRY(rst_tensor_alloc(c, C, C, &J));
+    GemmArgs gj{};                                   // -(Oᵀ·O): both operands are `output`, reduced over the batch
+    gj.A = output->data; gj.B = output->data; gj.C = J->data;
+    gj.M = C; gj.N = C; gj.K = B;
+    gj.a_kmajor = false; gj.b_kmajor = false;
+    gj.epilogue = kEpiDivN; gj.divisor = -1.0;
+    int s = launch_gemm(c, gj);
+    if (s == RST_OK) s = launch_softmax_jacobian_diag(c, J->data, C);
+    if (s == RST_OK) {
+        GemmArgs gx{};                               // gradient · jacobian
+        gx.A = gradient->data; gx.B = J->data; gx.C = dX->data;
+        gx.M = gradient->rows; gx.N = C; gx.K = C;
+        gx.a_kmajor = true; gx.b_kmajor = false;
+        gx.epilogue = kEpiNone; gx.divisor = 1.0;
+        s = launch_gemm(c, gx);
+    }
+    rst_tensor_free(J);      // stream-ordered: the block is reused only by later launches
+    return s;
+}
+
 extern "C" int rst_xent_slots(void) { return kXentSlots; }
 
 extern "C" int rst_xent_forward_backward(rst_ctx* c, const rst_tensor* logits, const rst_tensor* truth,

@@ -54,6 +54,41 @@ class KaimingNormal(InitParameters):
             output_size, input_size)
 
 
+class XavierNormal(InitParameters):
+    """N(0, sqrt(2 / (input_size + output_size))) weights (module/init/xavier.rs:9-15)."""
+
+    def __init__(self, seed: int = 0):
+        self.seed, self._layer = int(seed), 0
+
+    def weight(self, input_size: int, output_size: int) -> np.ndarray:
+        stream = synth.stream_key(self.seed, "xavier", self._layer)
+        self._layer += 1
+        sigma = np.sqrt(2.0 / (float(input_size) + float(output_size)))
+        return synth.normal(stream, output_size * input_size, std=sigma).reshape(output_size, input_size)
+
+
+class Normal(InitParameters):
+    """N(mean, std) weights (module/init/sigma.rs:7-37); `new` returns None for a
+    non-finite std, like the reference's `Option`."""
+
+    def __init__(self, mean: float, std: float, seed: int = 0):
+        self.mean, self.std, self.seed, self._layer = float(mean), float(std), int(seed), 0
+
+    @classmethod
+    def new(cls, mean: float, std: float, seed: int = 0) -> "Normal | None":
+        return cls(mean, std, seed) if np.isfinite(std) else None
+
+    @classmethod
+    def new_std(cls, std: float, seed: int = 0) -> "Normal | None":
+        return cls.new(0.0, std, seed)
+
+    def weight(self, input_size: int, output_size: int) -> np.ndarray:
+        stream = synth.stream_key(self.seed, "normal", self._layer)
+        self._layer += 1
+        return synth.normal(stream, output_size * input_size, std=self.std, mean=self.mean).reshape(
+            output_size, input_size)
+
+
 class Module:
     """`trait Module` (module/mod.rs:42-56)."""
 
@@ -114,6 +149,40 @@ class ReLU(Module):
                                "(the reference panics on `prev_input.take().unwrap()`, relu.rs:26)")
         prev, self.prev_input = self.prev_input, None
         return prev
+
+
+class Softmax(Module):
+    """Softmax as a layer (activation/softmax.rs:5-34, 55-78).  The backward is the
+    reference's, kept as written: a Jacobian `-(Oᵀ·O)` over the whole batch with the
+    diagonal replaced by s(1-s), applied as `gradient · jacobian` (softmax.rs:62-75)."""
+
+    def __init__(self, axis: int = 1):
+        if axis not in (0, 1):
+            raise IndexError(f"axis {axis} out of range for a 2-D array")
+        self.axis = axis
+        self.output: Tensor | None = None
+
+    @classmethod
+    def with_axis(cls, axis: int) -> "Softmax":
+        return cls(axis)
+
+    def forward(self, input: Tensor) -> Tensor:
+        ctx = input.ctx
+        out = ctx.empty(input.rows, input.cols)
+        fn = ctx._lib.rst_softmax if self.axis == 1 else ctx._lib.rst_softmax_axis0
+        ctx._check(fn(ctx.handle, input.handle, out.handle))
+        self.output = out
+        return out
+
+    def backward(self, gradient: Tensor) -> Tensor:
+        if self.output is None:
+            raise RuntimeError("Softmax::backward called without a preceding forward "
+                               "(the reference panics on `output.take().unwrap()`, softmax.rs:63)")
+        output, self.output = self.output, None
+        ctx = gradient.ctx
+        dx = ctx.empty(gradient.rows, output.cols)
+        ctx._check(ctx._lib.rst_softmax_backward(ctx.handle, output.handle, gradient.handle, dx.handle))
+        return dx
 
 
 class Linear(Module):

@@ -93,3 +93,23 @@ def test_dataset_errors(ctx):
     with pytest.raises(rt.RstError) as e:
         ds.gather(np.array([0, 1, 2]), X, T)
     assert e.value.status == _lib.RST_ERR_SHAPE
+
+
+def test_idx_files_to_device_batches(ctx, tmp_path):
+    """The README's input path end to end: IDX files on disk -> MNIST dataset -> HBM ->
+    `iter_array` batches of flatten(normalize_zero_one(x)) and one_hot(y, 10)."""
+    import struct
+
+    from rstorch_b200 import mnist
+    images, labels = synth.mnist_like_u8(5, 0, 96)
+    for name, arr in (("train-images-idx3-ubyte", images), ("train-labels-idx1-ubyte", labels)):
+        with open(tmp_path / name, "wb") as f:
+            f.write(struct.pack(">I", 8 * 256 + arr.ndim))
+            f.write(struct.pack(f">{arr.ndim}I", *arr.shape))
+            f.write(arr.tobytes())
+    train = mnist.MNIST(str(tmp_path), train=True)
+    loader = rt.DataLoader(train.to_device(ctx), 32, False, rt.SequentialSampler(len(train)), ctx)
+    for k, (x, t) in enumerate(loader.iter_array()):
+        want_x, want_t = on.iter_array_batch(images, labels, np.arange(k * 32, k * 32 + 32), 10)
+        assert np.array_equal(x.numpy(), want_x) and np.array_equal(t.numpy(), want_t)
+    assert k == 2

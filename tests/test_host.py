@@ -94,3 +94,50 @@ def test_one_hot():
     assert rt.one_hot(3, 5).tolist() == [0, 0, 0, 1, 0]
     with pytest.raises(IndexError):
         rt.one_hot(5, 5)
+
+
+def test_initialisers_follow_their_distributions():
+    w = rt.XavierNormal(seed=1).weight(300, 200)
+    assert w.shape == (200, 300) and abs(w.std() / np.sqrt(2.0 / 500.0) - 1.0) < 0.02 and abs(w.mean()) < 0.01
+    n = rt.Normal.new(2.0, 0.5, seed=1)
+    v = n.weight(400, 100)
+    assert v.shape == (100, 400) and abs(v.mean() - 2.0) < 0.01 and abs(v.std() - 0.5) < 0.01
+    assert rt.Normal.new(0.0, float("nan")) is None and rt.Normal.new_std(float("inf")) is None
+    assert np.array_equal(n.bias(400, 100), np.zeros((1, 100)))
+
+
+def _write_idx(path, array, type_code):
+    import struct
+    with open(path, "wb") as f:
+        f.write(struct.pack(">I", type_code * 256 + array.ndim))
+        f.write(struct.pack(f">{array.ndim}I", *array.shape))
+        f.write(array.astype(array.dtype.newbyteorder(">")).tobytes())
+
+
+def test_idx_reader_and_mnist_dataset(tmp_path):
+    from rstorch_b200 import mnist
+    images, labels = synth.mnist_like_u8(4, 0, 50)
+    _write_idx(tmp_path / "train-images-idx3-ubyte", images, 8)
+    _write_idx(tmp_path / "train-labels-idx1-ubyte", labels, 8)
+    ds = mnist.MNIST(str(tmp_path), train=True)
+    assert len(ds) == 50 and np.array_equal(ds.data, images) and np.array_equal(ds.labels, labels)
+    img, lab = ds.get(7)
+    assert img.shape == (28, 28) and img.dtype == np.uint8 and lab == labels[7] and ds.get(50) is None
+    with pytest.raises(FileNotFoundError):
+        mnist.MNIST(str(tmp_path), train=False)                       # the t10k files are not there
+    # big-endian multi-byte element types of the format (mnist.rs:258-263)
+    vals = np.array([[1, -2, 300], [-40000, 5, 6]], dtype=np.int32)
+    _write_idx(tmp_path / "i32", vals, 12)
+    assert np.array_equal(mnist.read_sn3(str(tmp_path / "i32")), vals)
+    f64 = np.array([1.5, -2.25, 1e300])
+    _write_idx(tmp_path / "f64", f64, 14)
+    assert np.array_equal(mnist.read_sn3(str(tmp_path / "f64"), ndim=1, type_code=14), f64)
+    # the reference asserts on the header (mnist.rs:284-285) and unwraps the reshape
+    with pytest.raises(ValueError):
+        mnist.read_image_file(str(tmp_path / "train-labels-idx1-ubyte"))
+    with pytest.raises(ValueError):
+        mnist.read_sn3(str(tmp_path / "i32"), type_code=8)
+    with open(tmp_path / "short", "wb") as f:
+        f.write(open(tmp_path / "train-images-idx3-ubyte", "rb").read()[:1000])
+    with pytest.raises(ValueError):
+        mnist.read_image_file(str(tmp_path / "short"))

@@ -44,6 +44,18 @@ def test_kat_softmax_rows(kat, oc):
     assert abs(p.sum() - k["expected_total"]) <= 4 * np.finfo(float).eps
 
 
+def test_kat_softmax_module(kat):
+    k = kat["softmax_axis0_columns_sum_to_one"]
+    p = on.softmax_axis(A(k["input"]), 0)
+    assert np.max(np.abs(p.sum(axis=0) - A(k["expected_column_sums"]))) <= kat["tolerance"]
+    assert abs(p.sum() - k["expected_total"]) <= 4 * np.finfo(float).eps
+    b = kat["softmax_module_backward"]
+    out = on.softmax_axis(A(b["input"]), 1)
+    got = on.softmax_module_backward(out, A(b["gradient"]))
+    assert np.max(np.abs(got - A(b["expected"]))) <= b["tolerance"]
+    assert np.array_equal(on.softmax_axis(A(b["input"]), 1), on.softmax(A(b["input"])))
+
+
 def test_kat_sgd_zero_gradient(kat, oc):
     k = kat["sgd_zero_gradient"]
     w = np.array([[0.3, -0.2], [1.5, 2.5]])
