@@ -54,6 +54,54 @@ __device__ __forceinline__ double apply_epilogue(const GemmParams& p, double v, 
     }
 }
 
+template <int W> __device__ __forceinline__ void load_run(double (&v)[W], const double* src);
+template <> __device__ __forceinline__ void load_run<2>(double (&v)[2], const double* src) {
+    const double2 x = *reinterpret_cast<const double2*>(src);
+    v[0] = x.x; v[1] = x.y;
+}
+template <> __device__ __forceinline__ void load_run<4>(double (&v)[4], const double* src) {
+    asm volatile("ld.global.v4.f64 {%0,%1,%2,%3}, [%4];" : "=d"(v[0]), "=d"(v[1]), "=d"(v[2]), "=d"(v[3]) : "l"(src));
+}
+template <int W> __device__ __forceinline__ void store_run(double* dst, const double (&v)[W]);
+template <> __device__ __forceinline__ void store_run<2>(double* dst, const double (&v)[2]) {
+    *reinterpret_cast<double2*>(dst) = make_double2(v[0], v[1]);
+}
+template <> __device__ __forceinline__ void store_run<4>(double* dst, const double (&v)[4]) {
+    asm volatile("st.global.v4.f64 [%0], {%1,%2,%3,%4};" ::"l"(dst), "d"(v[0]), "d"(v[1]), "d"(v[2]), "d"(v[3]) : "memory");
+}
+
+// Finishes W consecutive elements of row r starting at column c0: epilogue, then store.
+// With vec_ok (row pitch and bases aligned to the run) whole runs use one 16- or 32-byte
+// access per array; ragged edges and unaligned tensors take the element-wise path.
+template <int W>
+__device__ __forceinline__ void emit_run(const GemmParams& p, long long r, long long c0, double (&v)[W], bool vec_ok) {
+    double* dst = p.C + r * p.N + c0;
+    if (vec_ok && c0 + W <= p.N) {
+        if (p.epilogue == kEpiMask) {
+            double m[W];
+            load_run<W>(m, p.mask_src + r * p.N + c0);
+#pragma unroll
+            for (int i = 0; i < W; ++i) v[i] = v[i] * (m[i] > 0.0 ? 1.0 : 0.0);
+        } else if (p.epilogue == kEpiBias || p.epilogue == kEpiBiasRelu) {
+            double b[W];
+            load_run<W>(b, p.bias + c0);
+#pragma unroll
+            for (int i = 0; i < W; ++i) {
+                v[i] = v[i] + b[i];
+                if (p.epilogue == kEpiBiasRelu) v[i] = fmax(v[i], 0.0);
+            }
+        } else if (p.epilogue == kEpiDivN) {
+#pragma unroll
+            for (int i = 0; i < W; ++i) v[i] = v[i] / p.divisor;
+        }
+        store_run<W>(dst, v);
+    } else {
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+            if (c0 + i < p.N) dst[i] = apply_epilogue(p, v[i], r, c0 + i);
+    }
+}
+
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
 struct Cfg {
     static_assert(A_K || !B_K, "M-major A with K-major B is not used by Linear");
@@ -279,6 +327,9 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     const long long MN = p.M * p.N;
     if (p.splits == 1) {
+        constexpr int kRun = B_K ? 2 : 4;
+        const bool vec_ok = (p.N % kRun == 0) &&
+                            ((((uintptr_t)p.C | (uintptr_t)p.mask_src | (uintptr_t)p.bias) & (8 * kRun - 1)) == 0);
         if (ok) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
@@ -286,13 +337,24 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 for (int h = 0; h < 2; ++h) {
                     const long long r = row_of(mt, h);
                     if (r >= p.M) continue;
+                    // A thread owns runs of consecutive columns in a row: two per n-tile with
+                    // a K-major B, four per pair of n-tiles with an N-major B.  Each run is
+                    // finished (bias or mask loaded first, then one vector store) on its own,
+                    // so the epilogue's loads do not queue behind its stores.
+                    if (B_K) {
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const long long c = col_of(nt, e);
-                            if (c < p.N) p.C[r * p.N + c] = apply_epilogue(p, acc[mt][nt][2 * h + e], r, c);
+                        for (int nt = 0; nt < NT; ++nt) {
+                            double v[2] = {acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]};
+                            emit_run<2>(p, r, col_of(nt, 0), v, vec_ok);
                         }
+                    } else {
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt += 2) {
+                            double v[4] = {acc[mt][nt][2 * h], acc[mt][nt + 1][2 * h], acc[mt][nt][2 * h + 1],
+                                           acc[mt][nt + 1][2 * h + 1]};
+                            emit_run<4>(p, r, col_of(nt, 0), v, vec_ok);
+                        }
+                    }
                     if (FUSE_COLSUM) {
                         if (do_colsum && t == 0) p.colsum_out[r] = asum[mt][h] / p.divisor;
                     }

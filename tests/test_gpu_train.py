@@ -145,3 +145,45 @@ def test_wide_layer_sampled_entries_at_benchmark_size(ctx):
     y2 = lin.forward(ctx.tensor(2.0 * X)).numpy()
     assert np.array_equal(y2, 2.0 * y)
     ctx.check_device()
+
+
+def test_wide_mlp_full_size_step(ctx, oc):
+    """The wide-MLP workload at its own size (1024-4096-4096-4096-1000, batch 8192): one
+    whole step against the CPU restatement, every gradient and updated weight."""
+    dims, batch = [1024, 4096, 4096, 4096, 1000], 8192
+    w_cpu = [(w.copy(), b.copy()) for w, b in synth.mlp_weights(0, dims)]
+    model = build_mlp(ctx, dims, w_cpu, identity=False)
+    X, T = synth.gaussian_batch(0, 0, 0, batch, dims[0], dims[-1], batch)
+    loss_fn, opt = rt.CrossEntropyLoss(), rt.SGD.new(0.01)
+    pred = model.forward(ctx.tensor(X))
+    loss = loss_fn.forward(pred, ctx.tensor(T))
+    model.backward(loss_fn.backward(), need_input_grad=False)
+    opt.step(model)
+    losses, accs, grads = oc.mlp_train(dims, w_cpu, X, T, batch, 1, 0.01, skip_first_dx=True)
+    assert abs(loss - losses[0]) <= REL_TOL * abs(losses[0])
+    assert loss_fn.last_accuracy == accs[0]
+    for l, lin in enumerate(linears(model)):
+        assert rel_err(lin.grad_weight.numpy(), grads[l][0]) < REL_TOL, l
+        assert rel_err(lin.grad_bias.numpy(), grads[l][1]) < REL_TOL, l
+        assert rel_err(lin.weight.numpy(), w_cpu[l][0]) < REL_TOL, l
+        assert rel_err(lin.bias.numpy(), w_cpu[l][1]) < REL_TOL, l
+    ctx.check_device()
+
+
+def test_deep_mlp_reduced_width_trajectory(ctx, oc):
+    """The deep-MLP topology (input, ten Linear layers with ReLU between them, 1000 classes)
+    at reduced width and batch: three free-running steps against the restatement."""
+    dims, batch, steps = [256] + [512] * 9 + [1000], 512, 3
+    w_cpu = [(w.copy(), b.copy()) for w, b in synth.mlp_weights(2, dims)]
+    model = build_mlp(ctx, dims, w_cpu, identity=False)
+    loss_fn, opt = rt.CrossEntropyLoss(), rt.SGD.new(0.01)
+    for s in range(steps):
+        X, T = synth.gaussian_batch(2, s, 0, batch, dims[0], dims[-1], batch)
+        loss = loss_fn.forward(model.forward(ctx.tensor(X)), ctx.tensor(T))
+        model.backward(loss_fn.backward(), need_input_grad=False)
+        opt.step(model)
+        losses, accs, grads = oc.mlp_train(dims, w_cpu, X, T, batch, 1, 0.01, skip_first_dx=True)
+        assert abs(loss - losses[0]) <= REL_TOL * abs(losses[0]) and loss_fn.last_accuracy == accs[0]
+        for l, lin in enumerate(linears(model)):
+            assert rel_err(lin.grad_weight.numpy(), grads[l][0]) < REL_TOL, (s, l)
+            assert rel_err(lin.weight.numpy(), w_cpu[l][0]) < REL_TOL, (s, l)
