@@ -224,13 +224,20 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t a_box_off = (uint32_t)(wm * C_::WTM / 16) * kBoxBytes;         // + mt*2048
     const uint32_t b_box_off = (uint32_t)(wn * C_::WTN / 16) * kBoxBytes;         // + (nt/2)*2048
 
-    // Fragments of k sub-step i (0 or 1) of the stage at (As, Bs).
-    auto load_frags = [&](uint32_t As, uint32_t Bs, int i, double (&a)[MT][4], double (&b)[NT][2]) {
-        // rows of an M-/N-major tile that feed logical k = t and k = t+4 of this sub-step
+    // Rows of an M-/N-major tile that feed logical k = t and k = t+4 of sub-step i, as
+    // byte offsets inside a box; computed once, outside the k loop.
+    uint32_t mn_off[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
         const int kr0 = C_::kMnNatural ? (8 * i + 2 * t) : (4 * t + 2 * i);
         const int kr1 = kr0 + 1;
-        const uint32_t mn_off0 = (uint32_t)kr0 * kRowBytes + ((uint32_t)(g ^ (kr0 & 7)) << 4);
-        const uint32_t mn_off1 = (uint32_t)kr1 * kRowBytes + ((uint32_t)(g ^ (kr1 & 7)) << 4);
+        mn_off[i][0] = (uint32_t)kr0 * kRowBytes + ((uint32_t)(g ^ (kr0 & 7)) << 4);
+        mn_off[i][1] = (uint32_t)kr1 * kRowBytes + ((uint32_t)(g ^ (kr1 & 7)) << 4);
+    }
+
+    // Fragments of k sub-step i (0 or 1) of the stage at (As, Bs).
+    auto load_frags = [&](uint32_t As, uint32_t Bs, int i, double (&a)[MT][4], double (&b)[NT][2]) {
+        const uint32_t mn_off0 = mn_off[i][0], mn_off1 = mn_off[i][1];
         const uint32_t kchunk = kchunk0 ^ ((uint32_t)i << 4);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
