@@ -597,7 +597,10 @@ extern "C" int rst_graph_launch(rst_graph* g) {
 
 extern "C" int rst_graph_destroy(rst_graph* g) {
     if (!g) return RST_OK;
-    if (valid(g->ctx)) cudaStreamSynchronize(g->ctx->compute);
+    // Wait for replays in flight, unless the stream is recording another graph (a
+    // synchronisation would invalidate that capture; cudaGraphExecDestroy itself defers
+    // the release of an executable graph that is still running).
+    if (valid(g->ctx) && !g->ctx->capturing) cudaStreamSynchronize(g->ctx->compute);
     cudaGraphExecDestroy(g->exec);
     cudaGraphDestroy(g->graph);
     delete g;
