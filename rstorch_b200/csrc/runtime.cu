@@ -234,8 +234,14 @@ extern "C" int rst_ctx_create(int device, rst_ctx** out) {
     } while (0)
 
     CTX_CUDA(cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking));
-    CTX_CUDA(cudaStreamCreateWithFlags(&c->copy, cudaStreamNonBlocking));
-    CTX_CUDA(cudaStreamCreateWithFlags(&c->comm, cudaStreamNonBlocking));
+    {
+        // The collective's few CTAs must get an SM as soon as one frees up, ahead of the
+        // thousands of queued CTAs of the GEMM it overlaps with: highest stream priority.
+        int least = 0, greatest = 0;
+        CTX_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        CTX_CUDA(cudaStreamCreateWithPriority(&c->comm, cudaStreamNonBlocking, greatest));
+        CTX_CUDA(cudaStreamCreateWithPriority(&c->copy, cudaStreamNonBlocking, greatest));
+    }
     CTX_CUDA(cudaMalloc((void**)&c->d_status, 4 * sizeof(int)));
     CTX_CUDA(cudaMemset(c->d_status, 0, 4 * sizeof(int)));
     CTX_CUDA(cudaMallocHost((void**)&c->h_status, 4 * sizeof(int)));
