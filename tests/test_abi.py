@@ -30,6 +30,45 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert sorted(_lib.exported_symbols()) == names, "ctypes table and header disagree"
 
 
+def _split_args(arglist: str) -> list[str]:
+    arglist = arglist.strip()
+    return [] if arglist in ("", "void") else [a for a in arglist.split(",") if a.strip()]
+
+
+def test_rust_bindings_declare_the_same_entry_points():
+    """`bindings/rust/src/ffi.rs` cannot be compiled here (no Rust toolchain); this keeps its
+    `extern "C"` block in step with the header by name, argument count and, for the
+    value arguments, width (int / int64_t / uint64_t / double / size_t)."""
+    header = open(os.path.join(ROOT, "include", "rstorch_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    c_decls = {m.group(1): _split_args(m.group(2))
+               for m in re.finditer(r"\b(rst_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", header)}
+    rust = open(os.path.join(ROOT, "bindings", "rust", "src", "ffi.rs")).read()
+    rust = re.sub(r"//[^\n]*", "", rust)
+    block = rust[rust.index('extern "C" {'):]
+    block = block[:block.index("\n}\n")]
+    rs_decls = {m.group(1): _split_args(m.group(2))
+                for m in re.finditer(r"pub fn (rst_[a-z0-9_]+)\s*\(([^)]*)\)", block)}
+    assert sorted(rs_decls) == sorted(c_decls)
+    scalar = {"int": "c_int", "int64_t": "i64", "uint64_t": "u64", "double": "c_double", "size_t": "usize"}
+    for name, c_args in c_decls.items():
+        r_args = rs_decls[name]
+        assert len(r_args) == len(c_args), f"{name}: {len(c_args)} arguments in C, {len(r_args)} in Rust"
+        for c_arg, r_arg in zip(c_args, r_args):
+            r_type = r_arg.split(":", 1)[1].strip()
+            is_ptr = "*" in c_arg or "[" in c_arg
+            assert is_ptr == r_type.startswith("*"), f"{name}: `{c_arg.strip()}` against `{r_arg.strip()}`"
+            if not is_ptr:
+                c_type = c_arg.strip().rsplit(" ", 1)[0].replace("const ", "").strip()
+                assert scalar[c_type] == r_type, f"{name}: `{c_arg.strip()}` against `{r_arg.strip()}`"
+    # constants the façade relies on
+    for const in ("RST_BIAS_GRAD_NOALLOC_MAX_COLS", "RST_COMM_ID_BYTES"):
+        c_val = re.search(rf"#define {const} (\d+)", header).group(1)
+        assert re.search(rf"pub const {const}: \w+ = {c_val};", rust), const
+    for m in re.finditer(r"\b(RST_(?:OK|ERR_[A-Z_]+)) = (\d+)", header):
+        assert re.search(rf"pub const {m.group(1)}: c_int = {m.group(2)};", rust), m.group(1)
+
+
 def test_version_and_status_strings():
     lib = _lib.load()
     assert lib.rst_version() >> 16 == 0
