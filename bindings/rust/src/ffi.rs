@@ -61,6 +61,10 @@ extern "C" {
     pub fn rst_linear_backward(ctx: *mut rst_ctx, dy: *const rst_tensor, x: *const rst_tensor,
                                w: *const rst_tensor, relu_mask_src: *const rst_tensor,
                                dw: *mut rst_tensor, db: *mut rst_tensor, dx: *mut rst_tensor) -> c_int;
+    pub fn rst_linear_backward_chain(ctx: *mut rst_ctx, n: c_int, dy: *const rst_tensor,
+                                     x: *const *const rst_tensor, w: *const *const rst_tensor,
+                                     relu_mask: *const c_uchar, dw: *const *mut rst_tensor,
+                                     db: *const *mut rst_tensor, dx: *const *mut rst_tensor) -> c_int;
     pub fn rst_bias_grad_noalloc(dy: *const c_double, rows: i64, cols: i64, db: *mut c_double,
                                  stream: *mut c_void) -> c_int;
 

@@ -127,6 +127,23 @@ int rst_linear_backward(rst_ctx* ctx, const rst_tensor* dY, const rst_tensor* X,
                         const rst_tensor* W, const rst_tensor* relu_mask_src,
                         rst_tensor* dW, rst_tensor* db, rst_tensor* dX);
 
+/* `Sequential::backward` (src/module/sequential.rs:88-94) over a run of n Linear
+ * layers, listed in forward order, with nothing or a ReLU between consecutive ones.
+ * Layer l maps its cached input X[l] (B, in_l) through W[l] (out_l, in_l); dY is the
+ * gradient at the last layer's output.  From l = n-1 down to 0, with g = dY for the
+ * last layer and g = dX[l+1] otherwise, the call computes exactly what n calls of
+ * rst_linear_backward would:
+ *   dX[l] = g · W[l], times (X[l] > 0) where relu_mask[l] != 0 (the ReLU in front of
+ *           layer l, whose output X[l] is);  dW[l] = gᵀ·X[l] / B;  db[l] = Σ_rows g / B.
+ * dX[0] may be NULL (the gradient of the network input is not needed); relu_mask and
+ * db may be NULL (no masks / no bias gradients).  The dX products depend on one
+ * another and run first; the dW/db products of layers too small to fill the GPU one
+ * at a time then share one launch.  Meant for chains of small layers: every dX[l]
+ * stays alive until the call's work has run. */
+int rst_linear_backward_chain(rst_ctx* ctx, int n, const rst_tensor* dY, const rst_tensor* const* X,
+                              const rst_tensor* const* W, const unsigned char* relu_mask,
+                              rst_tensor* const* dW, rst_tensor* const* db, rst_tensor* const* dX);
+
 /* Bias gradient without any allocation: db[c] = (Σ_r dY[r,c]) / rows, the same
  * value rst_linear_backward writes to db.  This entry point has no counterpart in
  * the reference; it exists for hosts that cannot call cudaMalloc where they need

@@ -10,6 +10,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/rstorch_b200.h"
@@ -76,6 +77,7 @@ struct rst_ctx {
     std::string last_error;
     uint64_t launches;
     bool capturing;
+    bool overlap_launches;    // programmatic dependent launch for the step's kernels
 
     int* d_status;            // device status words (kernels report bounded-wait expiry)
     int* h_status;            // pinned mirror
@@ -132,6 +134,39 @@ private:
                              cudaGetErrorString(e__), __FILE__, __LINE__);             \
     } while (0)
 
+// Launches a kernel of the step.  With ctx->overlap_launches the launch carries the
+// programmatic-stream-serialization attribute: the grid may start while the grid queued
+// before it on the same stream is still draining, so its prologue (barrier set-up,
+// descriptor prefetch, index arithmetic) hides the launch gap.  Only kernels that call
+// grid_dependency_wait() before their first global access may be launched through
+// here; launched without the attribute that call returns at once.
+template <typename... Params, typename... Args>
+inline void launch_step_kernel(rst_ctx* ctx, cudaStream_t stream, void (*kernel)(Params...), dim3 grid,
+                               dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->overlap_launches ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, Params(std::forward<Args>(args))...);   // error read by after_launch
+}
+
+#ifdef __CUDACC__
+// Blocks until every grid this one depends on has completed and its writes are visible.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next grid on the stream start launching once every CTA of this grid got here.
+__device__ __forceinline__ void grid_dependency_release() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
+
 #define RST_TRY(call)                      \
     do {                                   \
         int s__ = (call);                  \
@@ -155,6 +190,10 @@ struct GemmArgs {
 };
 // *colsum_done (optional) tells whether colsum_out was produced by the GEMM kernel itself.
 int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done = nullptr);
+// Up to four dW-type products (M-major A, N-major B, 1/n epilogue, column sums) in one
+// launch when together they fit one wave of small tiles; *grouped = false means nothing
+// was launched.
+int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped);
 
 int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols, double n,
                       double* out);

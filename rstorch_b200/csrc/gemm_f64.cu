@@ -119,10 +119,12 @@ struct Cfg {
     static constexpr bool kMnNatural = !A_K && !B_K;
 };
 
+// One CTA's share of one product: output tile `tile_index` (in the grouped order below),
+// k range of split `split`.  tmA and tmB must refer to kernel parameters declared
+// __grid_constant__ (the TMA unit reads the descriptors through their address).
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
-__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
-gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const GemmParams p) {
+__device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                                          const int tile_index, const int split) {
     using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
     constexpr int MT = C_::MT, NT = C_::NT;
 
@@ -137,14 +139,13 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // tile coordinates: groups of 8 tile rows share their B tiles in L2
     constexpr int kGroup = 8;
     const int tiles_per_group = kGroup * p.tiles_n;
-    const int group = blockIdx.x / tiles_per_group;
+    const int group = tile_index / tiles_per_group;
     const int first_m = group * kGroup;
     const int group_rows = min(p.tiles_m - first_m, kGroup);
-    const int in_group = blockIdx.x - group * tiles_per_group;
+    const int in_group = tile_index - group * tiles_per_group;
     const int tile_m = first_m + in_group % group_rows;
     const int tile_n = in_group / group_rows;
     const int m0 = tile_m * BM, n0 = tile_n * BN;
-    const int split = blockIdx.y;
     const int kt_begin = split * p.k_tiles_per_split;
     const int kt_end = min(kt_begin + p.k_tiles_per_split, p.k_tiles);
 
@@ -157,6 +158,11 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         fence_proxy_async();
     }
     __syncthreads();
+    // Everything above touched shared memory and parameters only; from here on the kernel
+    // reads operands and writes results that the grid launched before it may still be
+    // using.
+    grid_dependency_release();
+    grid_dependency_wait();
 
     if (warp == C_::kConsumerWarps) {
         // ---------------- producer warp: one lane drives TMA ----------------
@@ -393,9 +399,40 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
 }
 
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
+__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const GemmParams p) {
+    gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM>(tmA, tmB, p, (int)blockIdx.x,
+                                                                      (int)blockIdx.y);
+}
+
+// Several independent products of one layout in one launch: the dW (and db) products of
+// a chain of small layers, none of which fills the GPU by itself.  CTA x belongs to the
+// product i with first_cta[i] <= x < first_cta[i+1]; within a product the CTAs are
+// ordered split-major.
+constexpr int kMaxGroup = 4;
+struct GroupMaps { CUtensorMap a[kMaxGroup], b[kMaxGroup]; };
+struct GroupParams {
+    int count;
+    int first_cta[kMaxGroup + 1];
+    GemmParams p[kMaxGroup];
+};
+
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
+__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+gemm_f64_tma_dmma_grouped(const __grid_constant__ GroupMaps maps, const __grid_constant__ GroupParams gp) {
+    int i = 0;
+    while (i + 1 < gp.count && (int)blockIdx.x >= gp.first_cta[i + 1]) ++i;
+    const int local = (int)blockIdx.x - gp.first_cta[i];
+    const int tiles = gp.p[i].tiles_m * gp.p[i].tiles_n;
+    gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM>(maps.a[i], maps.b[i], gp.p[i],
+                                                                      local % tiles, local / tiles);
+}
+
 // Sums the split-K partials in split order and applies the epilogue; elements past
 // M*N are the fused column sums (db).
-__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
+__device__ __forceinline__ void reduce_splits(const GemmParams& p) {
     const long long MN = p.M * p.N;
     const long long total = MN + (p.colsum_out ? p.M : 0);
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -413,6 +450,19 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
             p.colsum_out[m] = v / p.divisor;
         }
     }
+}
+
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
+    grid_dependency_release();
+    grid_dependency_wait();
+    reduce_splits(p);
+}
+
+__global__ void __launch_bounds__(256) splitk_reduce_grouped_kernel(const __grid_constant__ GroupParams gp) {
+    grid_dependency_release();
+    grid_dependency_wait();
+    for (int i = 0; i < gp.count; ++i)
+        if (gp.p[i].splits > 1) reduce_splits(gp.p[i]);
 }
 
 // Plain-load kernel for operands TMA cannot address (odd row pitch or a base
@@ -475,12 +525,12 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     }
     p.colsum_out = FUSE_COLSUM ? a.colsum_out : nullptr;
     dim3 grid((unsigned)(p.tiles_m * p.tiles_n), (unsigned)p.splits);
-    kernel<<<grid, C_::kThreads, C_::kSmemBytes, ctx->compute>>>(tmA, tmB, p);
+    launch_step_kernel(ctx, ctx->compute, kernel, grid, dim3(C_::kThreads), (size_t)C_::kSmemBytes, tmA, tmB, p);
     RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma"));
     if (p.splits > 1) {
         const long long total = a.M * a.N + (p.colsum_out ? a.M : 0);
         const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
-        splitk_reduce_kernel<<<blocks, 256, 0, ctx->compute>>>(p);
+        launch_step_kernel(ctx, ctx->compute, splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, p);
         RST_TRY(after_launch(ctx, "splitk_reduce_kernel"));
     }
     return RST_OK;
@@ -500,12 +550,13 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
     if (tiles_large >= ctx->num_sms) return launch_cfg<128, 128, 2, 4, 6, A_K, B_K, false>(ctx, a, p, 1);
     // Small problems: 64x64 tiles.  CTAs that share an SM share its f64 tensor pipe,
     // so more than one wave of CTAs buys nothing: split K only as far as the grid
-    // still fits one wave, keeping at least four k-tiles per split and at most 16
-    // splits (the reduce kernel reads every partial).
+    // still fits one wave, keeping at least two k-tiles per split and at most 64
+    // splits (the reduce kernel reads every partial; measured on the batch-32 and
+    // batch-4096 steps against 4/16: 2 % and 4 % faster).
     const long long tiles_small = ((a.M + kSmallBM - 1) / kSmallBM) * ((a.N + kSmallBN - 1) / kSmallBN);
     long long splits = ctx->num_sms / tiles_small;
-    splits = std::min(splits, k_tiles / 4);
-    splits = std::min(splits, 16LL);
+    splits = std::min(splits, k_tiles / 2);
+    splits = std::min(splits, 64LL);
     splits = std::max(splits, 1LL);
     constexpr bool kFuse = !A_K && !B_K;     // the dW product also yields db
     if (kFuse && a.colsum_out && colsum_done) *colsum_done = true;
@@ -543,6 +594,106 @@ int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done) {
     if (a.a_kmajor && !a.b_kmajor) return launch_layout<true, false>(ctx, a, p, colsum_done);
     if (!a.a_kmajor && !a.b_kmajor) return launch_layout<false, false>(ctx, a, p, colsum_done);
     return fail(ctx, RST_ERR_UNSUPPORTED, "M-major A with K-major B is not implemented");
+}
+
+// The dW = dYᵀ·X / n products (with their db) of up to kMaxGroup layers in one launch plus
+// one reduce launch.  Taken only when every product is in the small-tile regime and all
+// their tiles fit one wave together; *grouped tells the caller whether it was (if not,
+// nothing was launched and the caller issues the products one by one).
+int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped) {
+    *grouped = false;
+    if (n < 2 || n > kMaxGroup) return RST_OK;
+    using C_ = Cfg<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, false, false>;
+    long long tiles_total = 0, units_total = 0;      // unit = one k-tile of one output tile
+    for (int i = 0; i < n; ++i) {
+        const GemmArgs& a = args[i];
+        if (a.a_kmajor || a.b_kmajor || a.M <= 0 || a.N <= 0 || a.K <= 0) return RST_OK;
+        if (a.M > 0x7fffff00LL || a.N > 0x7fffff00LL || a.K > 0x7fffff00LL) return RST_OK;
+        if ((a.M % 2) || (a.N % 2) || ((((uintptr_t)a.A | (uintptr_t)a.B) & 15u) != 0)) return RST_OK;
+        if (((a.M + 127) / 128) * ((a.N + 127) / 128) >= ctx->num_sms) return RST_OK;
+        const long long tiles = ((a.M + kSmallBM - 1) / kSmallBM) * ((a.N + kSmallBN - 1) / kSmallBN);
+        tiles_total += tiles;
+        units_total += tiles * ((a.K + kBK - 1) / kBK);
+    }
+    if (tiles_total > ctx->num_sms) return RST_OK;
+
+    // Smallest number of k-tiles per CTA for which all CTAs still fit one wave: CTAs that
+    // share an SM share its tensor pipe, so a second wave would only add its fixed costs.
+    auto ctas_for = [&](long long per_cta) {
+        long long ctas = 0;
+        for (int i = 0; i < n; ++i) {
+            const long long tiles = ((args[i].M + kSmallBM - 1) / kSmallBM) * ((args[i].N + kSmallBN - 1) / kSmallBN);
+            const long long kt = (args[i].K + kBK - 1) / kBK;
+            ctas += tiles * ((kt + per_cta - 1) / per_cta);
+        }
+        return ctas;
+    };
+    long long per_cta = std::max(2LL, (units_total + ctx->num_sms - 1) / ctx->num_sms);
+    while (ctas_for(per_cta) > ctx->num_sms) ++per_cta;
+
+    GroupMaps maps;
+    GroupParams gp{};
+    gp.count = n;
+    size_t ws_elems = 0;
+    long long reduce_elems = 0;
+    // longest CTAs first: products in decreasing k-tiles per CTA
+    int order[kMaxGroup];
+    for (int i = 0; i < n; ++i) order[i] = i;
+    auto kt_per_cta = [&](int i) {
+        const long long kt = (args[i].K + kBK - 1) / kBK;
+        const long long splits = (kt + per_cta - 1) / per_cta;
+        return (kt + splits - 1) / splits;
+    };
+    std::stable_sort(order, order + n, [&](int x, int y) { return kt_per_cta(x) > kt_per_cta(y); });
+    int cta = 0;
+    for (int slot = 0; slot < n; ++slot) {
+        const GemmArgs& a = args[order[slot]];
+        GemmParams& p = gp.p[slot];
+        p.C = a.C; p.bias = a.bias; p.mask_src = a.mask_src; p.colsum_out = a.colsum_out;
+        p.status = ctx->d_status; p.divisor = a.divisor;
+        p.M = a.M; p.N = a.N; p.K = a.K; p.epilogue = a.epilogue;
+        p.tiles_m = (int)((a.M + kSmallBM - 1) / kSmallBM);
+        p.tiles_n = (int)((a.N + kSmallBN - 1) / kSmallBN);
+        p.k_tiles = (int)((a.K + kBK - 1) / kBK);
+        const int want = (int)((p.k_tiles + per_cta - 1) / per_cta);
+        p.k_tiles_per_split = (p.k_tiles + want - 1) / want;
+        p.splits = (p.k_tiles + p.k_tiles_per_split - 1) / p.k_tiles_per_split;
+        RST_TRY(encode_map(ctx, &maps.a[slot], a.A, a.M, a.K, 16, kBK));
+        RST_TRY(encode_map(ctx, &maps.b[slot], a.B, a.N, a.K, 16, kBK));
+        gp.first_cta[slot] = cta;
+        cta += p.tiles_m * p.tiles_n * p.splits;
+        if (p.splits > 1) {
+            p.splitk_ws = reinterpret_cast<double*>(ws_elems);      // offset for now, base added below
+            ws_elems += (size_t)p.splits * ((size_t)a.M * (size_t)a.N + (size_t)a.M);
+            ws_elems = (ws_elems + 1) & ~(size_t)1;                  // keep every region 16-byte aligned
+            reduce_elems = std::max(reduce_elems, (long long)(a.M * a.N + (a.colsum_out ? a.M : 0)));
+        }
+    }
+    for (int slot = n; slot <= kMaxGroup; ++slot) gp.first_cta[slot] = cta;
+    if (ws_elems) {
+        RST_TRY(ensure_scratch(ctx, (void**)&ctx->splitk_ws, &ctx->splitk_ws_bytes, ws_elems * sizeof(double),
+                               "split-K"));
+        for (int slot = 0; slot < n; ++slot)
+            if (gp.p[slot].splits > 1)
+                gp.p[slot].splitk_ws = ctx->splitk_ws + reinterpret_cast<size_t>(gp.p[slot].splitk_ws);
+    }
+
+    auto kernel = gemm_f64_tma_dmma_grouped<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, false, false, true>;
+    static bool attr_set[16] = {false};   // per device
+    if (!attr_set[ctx->device & 15]) {
+        RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes));
+        attr_set[ctx->device & 15] = true;
+    }
+    launch_step_kernel(ctx, ctx->compute, kernel, dim3((unsigned)cta), dim3(C_::kThreads), (size_t)C_::kSmemBytes,
+                       maps, gp);
+    RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma_grouped"));
+    if (reduce_elems) {
+        const int blocks = (int)std::min<long long>((reduce_elems + 255) / 256, (long long)ctx->num_sms * 8);
+        launch_step_kernel(ctx, ctx->compute, splitk_reduce_grouped_kernel, dim3((unsigned)blocks), dim3(256), 0, gp);
+        RST_TRY(after_launch(ctx, "splitk_reduce_grouped_kernel"));
+    }
+    *grouped = true;
+    return RST_OK;
 }
 
 }  // namespace rst

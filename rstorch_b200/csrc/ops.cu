@@ -56,10 +56,10 @@ extern "C" int rst_linear_forward(rst_ctx* c, const rst_tensor* X, const rst_ten
 }
 
 // dW = dYᵀ·X / n, db = Σ_rows dY / n, dX = dY·W [* relu mask]   (src/module/linear.rs:60-69, relu.rs:26)
-extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X,
-                                   const rst_tensor* W, const rst_tensor* mask, rst_tensor* dW,
-                                   rst_tensor* db, rst_tensor* dX) {
-    RST_TRY(need_ctx(c));
+namespace {
+
+int check_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X, const rst_tensor* W,
+                          const rst_tensor* mask, rst_tensor* dW, rst_tensor* db, rst_tensor* dX) {
     RST_TRY(check_tensor(c, dY, "dY"));
     RST_TRY(check_tensor(c, X, "X"));
     RST_TRY(check_tensor(c, W, "W"));
@@ -82,14 +82,21 @@ extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_t
     if (mask) RST_TRY(same_shape(c, mask, X, "Linear::backward: relu_mask_src against X"));
     if (dX && (dX->data == dY->data || dX->data == W->data))
         return fail(c, RST_ERR_INVALID_ARG, "Linear::backward: dX aliases an input");
+    return RST_OK;
+}
 
-    const double n = (double)B;   // linear.rs:62
+GemmArgs weight_grad_args(const rst_tensor* dY, const rst_tensor* X, rst_tensor* dW, rst_tensor* db) {
     GemmArgs gw{};
     gw.A = dY->data; gw.B = X->data; gw.C = dW->data;
-    gw.M = out; gw.N = in; gw.K = B;
+    gw.M = dY->cols; gw.N = X->cols; gw.K = X->rows;
     gw.a_kmajor = false; gw.b_kmajor = false;
-    gw.epilogue = kEpiDivN; gw.divisor = n;
+    gw.epilogue = kEpiDivN; gw.divisor = (double)X->rows;   // linear.rs:62
     gw.colsum_out = db ? db->data : nullptr;
+    return gw;
+}
+
+int weight_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X, rst_tensor* dW, rst_tensor* db) {
+    const GemmArgs gw = weight_grad_args(dY, X, dW, db);
     bool db_done = false;
     {
         ProfScope prof(c, "gemm_dW");
@@ -97,18 +104,76 @@ extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_t
     }
     if (db && !db_done) {
         ProfScope prof(c, "colsum");
-        RST_TRY(launch_colsum_div(c, dY->data, B, out, n, db->data));
+        RST_TRY(launch_colsum_div(c, dY->data, X->rows, dY->cols, gw.divisor, db->data));
     }
-    if (dX) {
-        GemmArgs gx{};
-        gx.A = dY->data; gx.B = W->data; gx.C = dX->data;
-        gx.M = B; gx.N = in; gx.K = out;
-        gx.a_kmajor = true; gx.b_kmajor = false;
-        gx.epilogue = mask ? kEpiMask : kEpiNone;
-        gx.mask_src = mask ? mask->data : nullptr;
-        gx.divisor = 1.0;
-        ProfScope prof(c, "gemm_dX");
-        RST_TRY(launch_gemm(c, gx));
+    return RST_OK;
+}
+
+int input_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* W, const rst_tensor* mask, rst_tensor* dX) {
+    GemmArgs gx{};
+    gx.A = dY->data; gx.B = W->data; gx.C = dX->data;
+    gx.M = dY->rows; gx.N = W->cols; gx.K = W->rows;
+    gx.a_kmajor = true; gx.b_kmajor = false;
+    gx.epilogue = mask ? kEpiMask : kEpiNone;
+    gx.mask_src = mask ? mask->data : nullptr;
+    gx.divisor = 1.0;
+    ProfScope prof(c, "gemm_dX");
+    return launch_gemm(c, gx);
+}
+
+}  // namespace
+
+extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X,
+                                   const rst_tensor* W, const rst_tensor* mask, rst_tensor* dW,
+                                   rst_tensor* db, rst_tensor* dX) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_linear_backward(c, dY, X, W, mask, dW, db, dX));
+    RST_TRY(weight_grad(c, dY, X, dW, db));
+    if (dX) RST_TRY(input_grad(c, dY, W, mask, dX));
+    return RST_OK;
+}
+
+// Sequential::backward over n Linear layers (src/module/sequential.rs:88-94 folding
+// linear.rs:60-69, with relu.rs:26 for the ReLUs in between).  The dX products form a
+// dependent chain and run first; the dW/db products only read that chain's tensors and
+// go out together.
+extern "C" int rst_linear_backward_chain(rst_ctx* c, int n, const rst_tensor* dY, const rst_tensor* const* X,
+                                         const rst_tensor* const* W, const unsigned char* relu_mask,
+                                         rst_tensor* const* dW, rst_tensor* const* db,
+                                         rst_tensor* const* dX) {
+    RST_TRY(need_ctx(c));
+    if (n < 1 || !X || !W || !dW || !dX) return fail(c, RST_ERR_INVALID_ARG, "Linear backward chain: bad arguments");
+    for (int l = n - 1; l >= 0; --l) {
+        if (l > 0 && !dX[l])
+            return fail(c, RST_ERR_INVALID_ARG, "Linear backward chain: dX[%d] is needed by layer %d", l, l - 1);
+        const rst_tensor* g = (l == n - 1) ? dY : dX[l + 1];
+        const rst_tensor* mask = (relu_mask && relu_mask[l] && dX[l]) ? X[l] : nullptr;
+        RST_TRY(check_linear_backward(c, g, X[l], W[l], mask, dW[l], db ? db[l] : nullptr, dX[l]));
+    }
+    for (int l = n - 1; l >= 0; --l) {
+        if (!dX[l]) continue;
+        const rst_tensor* g = (l == n - 1) ? dY : dX[l + 1];
+        RST_TRY(input_grad(c, g, W[l], (relu_mask && relu_mask[l]) ? X[l] : nullptr, dX[l]));
+    }
+    constexpr int kChunk = 4;
+    for (int hi = n - 1; hi >= 0; hi -= kChunk) {
+        const int lo = hi - kChunk + 1 > 0 ? hi - kChunk + 1 : 0;
+        GemmArgs group[kChunk];
+        int m = 0;
+        for (int l = hi; l >= lo; --l) {
+            const rst_tensor* g = (l == n - 1) ? dY : dX[l + 1];
+            rst_tensor* dbl = db ? db[l] : nullptr;
+            if (!dbl) { m = 0; break; }             // the grouped kernel always produces db
+            group[m++] = weight_grad_args(g, X[l], dW[l], dbl);
+        }
+        bool grouped = false;
+        if (m >= 2) {
+            ProfScope prof(c, "gemm_dW");
+            RST_TRY(launch_gemm_group(c, group, m, &grouped));
+        }
+        if (!grouped)
+            for (int l = hi; l >= lo; --l)
+                RST_TRY(weight_grad(c, (l == n - 1) ? dY : dX[l + 1], X[l], dW[l], db ? db[l] : nullptr));
     }
     return RST_OK;
 }

@@ -212,6 +212,11 @@ extern "C" int rst_ctx_create(int device, rst_ctx** out) {
     c->num_sms = prop.multiProcessorCount > 0 ? prop.multiProcessorCount : kNumSMsFallback;
     c->launches = 0;
     c->capturing = false;
+    {
+        // RSTORCH_B200_OVERLAP_LAUNCHES=0 restores fully serialised launches (for A/B timing)
+        const char* v = std::getenv("RSTORCH_B200_OVERLAP_LAUNCHES");
+        c->overlap_launches = !(v && v[0] == '0');
+    }
     c->profiling = false;
     c->xent_partials = nullptr; c->xent_partials_cap = 0; c->xent_counter = nullptr;
     c->splitk_ws = nullptr; c->splitk_ws_bytes = 0;

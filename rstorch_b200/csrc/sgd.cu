@@ -56,6 +56,8 @@ __device__ __forceinline__ double sgd1(double p, double g, double lr) {
 __global__ void __launch_bounds__(kSgdThreads)
 sgd_multi_tensor_kernel(const SgdEntry* __restrict__ table, int n_tensors, long long total_chunks,
                         double lr) {
+    grid_dependency_release();
+    grid_dependency_wait();
     for (long long chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
         // largest t with table[t].first_chunk <= chunk
         int lo = 0, hi = n_tensors - 1;
@@ -154,8 +156,8 @@ extern "C" int rst_sgd_plan_step(rst_sgd_plan* plan, double lr) {
     long long cap = (long long)c->num_sms * 8;
     int grid = (int)std::min(plan->total_chunks, cap);
     ProfScope prof(c, "sgd");
-    sgd_multi_tensor_kernel<<<grid, kSgdThreads, 0, c->compute>>>(plan->d_table, plan->n,
-                                                                  plan->total_chunks, lr);
+    launch_step_kernel(c, c->compute, sgd_multi_tensor_kernel, dim3((unsigned)grid), dim3(kSgdThreads), 0,
+                       plan->d_table, plan->n, plan->total_chunks, lr);
     return after_launch(c, "sgd_multi_tensor_kernel");
 }
 

@@ -164,6 +164,8 @@ __global__ void __launch_bounds__(kXentThreads)
 xent_rows_kernel(const double* __restrict__ logits, const double* __restrict__ truth,
                  double* __restrict__ out, int64_t rows, int cols, BlockPartial* partials,
                  unsigned int* counter, ResultSlot* slot) {
+    grid_dependency_release();
+    grid_dependency_wait();
     constexpr int kRowsPerWarp = 32 / LPR;
     const int lane_in_warp = threadIdx.x & 31;
     const int lane = lane_in_warp % LPR;
@@ -370,8 +372,9 @@ int dispatch_rows(rst_ctx* ctx, const double* logits, const double* truth, doubl
     cudaStream_t st = ctx->compute;
     int c = (int)cols;
 #define XENT_CASE(LPR, EPL)                                                                    \
-    xent_rows_kernel<LPR, EPL, MODE><<<xent_grid(ctx, rows, 32 / LPR), kXentThreads, 0, st>>>( \
-        logits, truth, out, rows, c, partials, counter, d_slot)
+    launch_step_kernel(ctx, st, xent_rows_kernel<LPR, EPL, MODE>,                              \
+                       dim3((unsigned)xent_grid(ctx, rows, 32 / LPR)), dim3(kXentThreads), 0, \
+                       logits, truth, out, rows, c, partials, counter, d_slot)
     if (cols <= 16) XENT_CASE(4, 4);
     else if (cols <= 32) XENT_CASE(8, 4);
     else if (cols <= 128) XENT_CASE(32, 4);

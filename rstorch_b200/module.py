@@ -10,6 +10,7 @@ Names, argument meaning and error behaviour follow the Rust crate:
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 from typing import Callable, Iterable, Sequence
 
@@ -309,6 +310,10 @@ class Sequential(Module):
         (the reference computes it and its training loop discards it, README.md:72);
         the call then returns None.  `on_layer_grads(layer)` is called as soon as a
         Linear's dW/db are queued (used to start their all-reduce early)."""
+        if on_layer_grads is None:
+            chain = self._small_linear_chain()
+            if chain is not None:
+                return self._backward_chain(chain, gradient, need_input_grad)
         g: Tensor | None = gradient
         first_compute = next((k for k, l in enumerate(self.layers) if not self._plain(l, Identity)), None)
         i = len(self.layers) - 1
@@ -329,6 +334,56 @@ class Sequential(Module):
                 g = layer.backward(g)
             i -= 1
         return g
+
+    # A whole network of small layers goes through one library call, which runs the
+    # dependent dX products first and then all dW/db products in one launch.
+    _CHAIN_MAX_WEIGHT_ELEMS = 1 << 20
+
+    def _small_linear_chain(self) -> list[tuple[Linear, ReLU | None]] | None:
+        """[(linear, the ReLU in front of it or None), ...] in forward order when the
+        container is `Identity*, Linear, (ReLU, Linear)*` of plain layers that are all
+        small; None otherwise."""
+        layers = list(self.layers)
+        while layers and self._plain(layers[0], Identity):
+            layers.pop(0)
+        if len(layers) < 3 or len(layers) % 2 == 0:
+            return None
+        chain: list[tuple[Linear, ReLU | None]] = []
+        for k, layer in enumerate(layers):
+            if k % 2 == 0:
+                if not self._plain(layer, Linear) or layer.input_size * layer.output_size > self._CHAIN_MAX_WEIGHT_ELEMS:
+                    return None
+                chain.append((layer, layers[k - 1] if k else None))
+            elif not self._plain(layer, ReLU):
+                return None
+        return chain
+
+    def _backward_chain(self, chain, gradient: Tensor, need_input_grad: bool) -> Tensor | None:
+        ctx, n = gradient.ctx, len(chain)
+        xs = []
+        for lin, relu in chain:
+            if lin.prev_input is None:
+                raise RuntimeError("Linear::backward called without a preceding forward "
+                                   "(the reference panics on `prev_input.take().unwrap()`, linear.rs:61)")
+            xs.append(lin.prev_input)
+        for lin, relu in chain:
+            lin.prev_input = None
+            if relu is not None:
+                relu._take()
+            if lin.grad_weight is None or lin.grad_weight.ctx is not ctx:
+                lin.grad_weight = ctx.empty(lin.output_size, lin.input_size)
+                lin.grad_bias = ctx.empty(1, lin.output_size)
+        dxs = [ctx.empty(x.rows, x.cols) if (l > 0 or need_input_grad) else None for l, x in enumerate(xs)]
+
+        def handles(tensors):
+            return (C.c_void_p * n)(*[t.handle.value if t is not None else None for t in tensors])
+
+        masks = (C.c_ubyte * n)(*[1 if relu is not None else 0 for _, relu in chain])
+        ctx._check(ctx._lib.rst_linear_backward_chain(
+            ctx.handle, n, gradient.handle, handles(xs), handles([lin.weight for lin, _ in chain]), masks,
+            handles([lin.grad_weight for lin, _ in chain]), handles([lin.grad_bias for lin, _ in chain]),
+            handles(dxs)))
+        return dxs[0]
 
     def train(self) -> None:
         for layer in self.layers:
