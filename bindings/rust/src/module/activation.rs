@@ -30,6 +30,11 @@ impl Module for Identity {
     fn parameters(&mut self) -> Parameters<'_> {
         Parameters::new(0)
     }
+
+    #[inline]
+    fn fusion_role(&self) -> FusionRole {
+        FusionRole::Identity
+    }
 }
 
 /// `max(x, 0)`; backward multiplies by `(x > 0)` (relu.rs:17-32).  The cache is any tensor

@@ -57,6 +57,25 @@ impl Linear {
         self.grad_bias.as_ref()
     }
 
+    /// Number of weight elements, for `Sequential`'s "small layer" test.
+    pub(crate) fn weight_elems(&self) -> usize {
+        self.weight.nrows() * self.weight.ncols()
+    }
+
+    /// What the whole-chain backward needs from this layer: the cached input (taken, with
+    /// the reference's panic when it is missing, linear.rs:61) and the handles of W, dW, db.
+    pub(crate) fn chain_slot(&mut self) -> (Tensor, *const ffi::rst_tensor, *mut ffi::rst_tensor, *mut ffi::rst_tensor) {
+        let x = self.prev_input.take().unwrap();
+        let ctx = x.context().clone();
+        let (out_size, in_size) = (self.weight.nrows(), self.weight.ncols());
+        let dw = self.grad_weight.get_or_insert_with(|| ctx.empty(out_size, in_size)).raw();
+        let db = match &self.bias {
+            Some(_) => self.grad_bias.get_or_insert_with(|| ctx.empty(1, out_size)).raw(),
+            None => std::ptr::null_mut(),
+        };
+        (x, self.weight.raw() as *const ffi::rst_tensor, dw, db)
+    }
+
     fn run_forward(&mut self, input: Tensor, relu: bool) -> Tensor {
         let ctx = input.context().clone();
         let out = ctx.empty(input.nrows(), self.weight.nrows());
@@ -111,6 +130,11 @@ impl Module for Linear {
     #[inline]
     fn fusion_role(&self) -> FusionRole {
         FusionRole::Linear
+    }
+
+    #[inline]
+    fn as_linear(&mut self) -> Option<&mut Linear> {
+        Some(self)
     }
 
     #[inline]

@@ -47,6 +47,7 @@ impl<'a> Parameters<'a> {
 #[derive(Clone, Copy, Debug, PartialEq, Eq)]
 pub enum FusionRole {
     Other,
+    Identity,
     Linear,
     ReLU,
 }
@@ -84,6 +85,12 @@ pub trait Module {
     #[doc(hidden)]
     fn backward_fused(&mut self, gradient: Tensor, _relu_before: bool) -> Tensor {
         self.backward(gradient)
+    }
+
+    /// `Linear` only: the layer itself, for the whole-chain backward of `Sequential`.
+    #[doc(hidden)]
+    fn as_linear(&mut self) -> Option<&mut Linear> {
+        None
     }
 
     /// `ReLU` only: the layer in front produced `output` with this ReLU already applied;

@@ -8,8 +8,12 @@
 //! own keep the unfused kernels.
 use std::fmt::Debug;
 
+use crate::ffi;
 use crate::module::{FusionRole, Module, Parameters};
 use crate::tensor::Tensor;
+
+/// Layers above this many weight elements keep the layer-by-layer backward.
+const CHAIN_MAX_WEIGHT_ELEMS: usize = 1 << 20;
 
 pub trait ModuleDebug: Module + Debug {}
 impl<T: Module + Debug> ModuleDebug for T {}
@@ -71,6 +75,57 @@ impl Sequential {
     fn role(&self, index: usize) -> FusionRole {
         self.layers[index].fusion_role()
     }
+
+    /// Index of the first layer of a trailing `Linear, (ReLU, Linear)*` run of small plain
+    /// layers that, apart from leading `Identity` layers, is the whole container.
+    fn small_linear_chain(&mut self) -> Option<usize> {
+        let first = (0..self.layers.len()).find(|&i| self.role(i) != FusionRole::Identity)?;
+        let n = self.layers.len() - first;
+        if n < 3 || n % 2 == 0 {
+            return None;
+        }
+        for k in 0..n {
+            if k % 2 == 0 {
+                let small = self.layers[first + k].as_linear().map(|l| l.weight_elems() <= CHAIN_MAX_WEIGHT_ELEMS);
+                if small != Some(true) {
+                    return None;
+                }
+            } else if self.role(first + k) != FusionRole::ReLU {
+                return None;
+            }
+        }
+        Some(first)
+    }
+
+    /// The whole backward as one library call: the dependent dX products first, then every
+    /// dW/db product in one launch.
+    fn backward_chain(&mut self, first: usize, gradient: &Tensor) -> Tensor {
+        let n = (self.layers.len() - first + 1) / 2;
+        let ctx = gradient.context().clone();
+        let (mut xs, mut dxs) = (Vec::with_capacity(n), Vec::with_capacity(n));
+        let (mut hx, mut hw, mut hdw, mut hdb, mut hdx, mut mask) =
+            (Vec::new(), Vec::new(), Vec::new(), Vec::new(), Vec::new(), Vec::new());
+        for l in 0..n {
+            if l > 0 {
+                self.layers[first + 2 * l - 1].discard_cache();
+            }
+            let (x, w, dw, db) = self.layers[first + 2 * l].as_linear().unwrap().chain_slot();
+            let dx = x.empty_like();
+            hx.push(x.raw() as *const ffi::rst_tensor);
+            hw.push(w);
+            hdw.push(dw);
+            hdb.push(db);
+            hdx.push(dx.raw());
+            mask.push(u8::from(l > 0));
+            xs.push(x);
+            dxs.push(dx);
+        }
+        ctx.check(unsafe {
+            ffi::rst_linear_backward_chain(ctx.raw(), n as i32, gradient.raw(), hx.as_ptr(), hw.as_ptr(),
+                                           mask.as_ptr(), hdw.as_ptr(), hdb.as_ptr(), hdx.as_ptr())
+        });
+        dxs.swap_remove(0)
+    }
 }
 
 #[macro_export]
@@ -102,6 +157,9 @@ impl Module for Sequential {
     }
 
     fn backward(&mut self, gradient: Tensor) -> Tensor {
+        if let Some(first) = self.small_linear_chain() {
+            return self.backward_chain(first, &gradient);
+        }
         let mut g = gradient;
         let mut i = self.layers.len();
         while i > 0 {

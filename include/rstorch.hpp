@@ -248,6 +248,7 @@ public:
         Tensor g = std::move(gradient);
         size_t first = 0;
         while (first < layers_.size() && plain<Identity>(first)) ++first;
+        if (small_linear_chain(first)) return backward_chain(first, g, need_input_grad);
         for (size_t k = layers_.size(); k-- > 0;) {
             if (Linear* lin = plain<Linear>(k)) {
                 ReLU* before = k > 0 ? plain<ReLU>(k - 1) : nullptr;
@@ -271,6 +272,55 @@ private:
     template <class T> T* plain(size_t i) {              // exact type only: subclasses may override behaviour
         Module* m = layers_[i].get();
         return typeid(*m) == typeid(T) ? static_cast<T*>(m) : nullptr;
+    }
+    // `Linear, (ReLU, Linear)*` of plain small layers from `first` to the end: the whole
+    // backward is one library call (dX chain first, then every dW/db in one launch).
+    static constexpr size_t kChainMaxWeightElems = size_t(1) << 20;
+    bool small_linear_chain(size_t first) {
+        const size_t n = layers_.size() - first;
+        if (n < 3 || n % 2 == 0) return false;
+        for (size_t k = 0; k < n; ++k) {
+            if (k % 2 == 0) {
+                Linear* lin = plain<Linear>(first + k);
+                if (!lin || lin->in_ * lin->out_ > kChainMaxWeightElems) return false;
+            } else if (!plain<ReLU>(first + k)) {
+                return false;
+            }
+        }
+        return true;
+    }
+    Tensor backward_chain(size_t first, const Tensor& gradient, bool need_input_grad) {
+        std::vector<Linear*> lins;
+        for (size_t k = first; k < layers_.size(); k += 2) lins.push_back(plain<Linear>(k));
+        const int n = (int)lins.size();
+        std::vector<Tensor> xs(n), dxs(n);
+        for (int l = 0; l < n; ++l) {
+            if (!lins[l]->prev_input)
+                throw Panic(RST_ERR_STATE, "Linear::backward without a preceding forward (linear.rs:61 unwrap)");
+            xs[l] = lins[l]->prev_input;
+        }
+        std::vector<const rst_tensor*> hx(n), hw(n);
+        std::vector<rst_tensor*> hdw(n), hdb(n), hdx(n);
+        std::vector<unsigned char> mask(n);
+        for (int l = 0; l < n; ++l) {
+            Linear* lin = lins[l];
+            lin->prev_input = Tensor();
+            if (l > 0) plain<ReLU>(first + 2 * (size_t)l - 1)->take();
+            if (!lin->grad_weight) {
+                lin->grad_weight = Tensor::like(xs[l], (int64_t)lin->out_, (int64_t)lin->in_);
+                lin->grad_bias = Tensor::like(xs[l], 1, (int64_t)lin->out_);
+            }
+            if (l > 0 || need_input_grad) dxs[l] = Tensor::like(xs[l], xs[l].nrows(), xs[l].ncols());
+            hx[l] = xs[l].handle();
+            hw[l] = lin->weight.handle();
+            hdw[l] = lin->grad_weight.handle();
+            hdb[l] = lin->grad_bias.handle();
+            hdx[l] = dxs[l] ? dxs[l].handle() : nullptr;
+            mask[l] = l > 0 ? 1 : 0;
+        }
+        check(gradient.ctx(), rst_linear_backward_chain(gradient.ctx(), n, gradient.handle(), hx.data(), hw.data(),
+                                                        mask.data(), hdw.data(), hdb.data(), hdx.data()));
+        return dxs[0];
     }
     std::vector<std::unique_ptr<Module>> layers_;
 };

@@ -557,6 +557,7 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
     long long splits = ctx->num_sms / tiles_small;
     splits = std::min(splits, k_tiles / 2);
     splits = std::min(splits, 64LL);
+    if (k_tiles < 16) splits = 1;            // the reduce launch would cost more than the split saves
     splits = std::max(splits, 1LL);
     constexpr bool kFuse = !A_K && !B_K;     // the dW product also yields db
     if (kFuse && a.colsum_out && colsum_done) *colsum_done = true;

@@ -113,8 +113,10 @@ def test_fused_and_unfused_paths_agree(ctx):
         g = layer.backward(g)
     assert l1 == l2
     assert np.array_equal(dx1.numpy(), g.numpy())
+    # the container sends all dW products out in one grouped launch, which may cut the batch
+    # dimension into other split-K pieces than a single product does: same sums, other order
     for a, b in zip(fused.parameters(), plain.parameters()):
-        assert np.array_equal(a.grad.numpy(), b.grad.numpy())
+        assert rel_err(a.grad.numpy(), b.grad.numpy()) < 1e-13
 
 
 def test_wide_layer_sampled_entries_at_benchmark_size(ctx):
