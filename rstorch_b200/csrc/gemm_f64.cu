@@ -542,6 +542,7 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
 // SM has to keep enough bytes in flight to cover the latency of operands that are not
 // in L2 yet; a TMA tile load takes about 1.5 us even from L2).
 constexpr int kSmallBM = 64, kSmallBN = 64, kSmallWM = 2, kSmallWN = 4, kSmallStages = 8;
+constexpr int kTinyB = 32;
 
 template <bool A_K, bool B_K>
 int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_done) {
@@ -553,15 +554,25 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
     // still fits one wave, keeping at least two k-tiles per split and at most 64
     // splits (the reduce kernel reads every partial; measured on the batch-32 and
     // batch-4096 steps against 4/16: 2 % and 4 % faster).
-    const long long tiles_small = ((a.M + kSmallBM - 1) / kSmallBM) * ((a.N + kSmallBN - 1) / kSmallBN);
-    long long splits = ctx->num_sms / tiles_small;
-    splits = std::min(splits, k_tiles / 2);
-    splits = std::min(splits, 64LL);
-    if (k_tiles < 16) splits = 1;            // the reduce launch would cost more than the split saves
-    splits = std::max(splits, 1LL);
+    auto splits_for = [&](long long tiles) {
+        long long splits = ctx->num_sms / tiles;
+        splits = std::min(splits, k_tiles / 2);
+        splits = std::min(splits, 64LL);
+        if (k_tiles < 16) splits = 1;        // the reduce launch would cost more than the split saves
+        return (int)std::max(splits, 1LL);
+    };
     constexpr bool kFuse = !A_K && !B_K;     // the dW product also yields db
     if (kFuse && a.colsum_out && colsum_done) *colsum_done = true;
-    return launch_cfg<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, A_K, B_K, kFuse>(ctx, a, p, (int)splits);
+    // A product with at most 32 rows or columns (batch 32; the 10-class output layer) only
+    // fills a quarter of a 64x64 tile, and on a dependent chain of such launches the time
+    // of a k-tile is what counts: 32x32 tiles, one consumer warp per SM sub-partition,
+    // finish a k-tile in a quarter of the tensor-pipe time.
+    const long long tiles_tiny = ((a.M + kTinyB - 1) / kTinyB) * ((a.N + kTinyB - 1) / kTinyB);
+    if ((a.M <= kTinyB || a.N <= kTinyB) && tiles_tiny <= ctx->num_sms)
+        return launch_cfg<kTinyB, kTinyB, 2, 2, kSmallStages, A_K, B_K, kFuse>(ctx, a, p, splits_for(tiles_tiny));
+    const long long tiles_small = ((a.M + kSmallBM - 1) / kSmallBM) * ((a.N + kSmallBN - 1) / kSmallBN);
+    return launch_cfg<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, A_K, B_K, kFuse>(ctx, a, p,
+                                                                                              splits_for(tiles_small));
 }
 
 }  // namespace
