@@ -47,6 +47,19 @@ WORKLOAD_NAMES = {
     "c5": "fused SGD step over 2^30 f64 parameters in 64 tensors",
 }
 LR = 0.01
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant GEMM launch, from the ncu
+# captures summarised under profiles/ (bytes per launch), keyed by (workload, rows per GPU).
+# A GEMM's DRAM traffic depends on its shape, so other shapes report null rather than a
+# scaled guess.
+NCU_GEMM_TRAFFIC = {
+    ("c4", 65536): {"bytes": 66.9e9,
+                    "note": "forward 65536x8192x8192: 62.5 GB read + 4.36 GB written against 9.1 GB "
+                            "compulsory, 270 GB/s = 4 % of HBM bandwidth (profiles/gemm_f64_tma_dmma_c4_traffic.md)"},
+    ("c3", 8192): {"bytes": 2.06e9,
+                   "note": "forward 8192x4096x4096: 1.80 GB read + 0.26 GB written against 0.67 GB compulsory "
+                           "(profiles/gemm_f64_tma_dmma_c3.md)"},
+}
 SEED = 0
 L2_BYTES = 126 << 20
 
@@ -432,11 +445,13 @@ def mlp_arm(args) -> None:
     peaks = read_measured_peaks()
     fp64_peak = ctx.probe_fp64_peak(0, 2048)
     achieved = flops_step_local / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    traffic = NCU_GEMM_TRAFFIC.get((wl, rows))
     roofline = {
         "bound": "tensor", "kernel": "gemm_f64_tma_dmma",
         "achieved": achieved, "peak": fp64_peak, "unit": "TFLOP/s",
         "frac": achieved / fp64_peak if achieved else None,
-        "traffic": None,
+        "traffic": traffic["bytes"] if traffic else None,
+        "traffic_note": traffic["note"] if traffic else "no ncu capture at this shape",
         "peak_source": "f64 DMMA issue-rate probe run in this process (MEASURED_PEAKS.json records no f64 "
                        "figure; its bf16 peak does not bound an f64 kernel)",
         "launches_per_step": gemm_launches, "kernel_ms_per_step": gemm_ms,
@@ -527,7 +542,11 @@ def sgd_arm(args) -> None:
                    "l2": "inputs larger than L2"},
         "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "sgd_multi_tensor_kernel", "achieved": achieved, "peak": hbm_peak,
-                     "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / hbm_peak,
+                     # ncu on a 2^27-parameter launch: 3.18 GB moved against 3.22 GB algorithmic; an
+                     # elementwise kernel's traffic grows in proportion to the parameter count
+                     "traffic": 24.0 * total * (3.184 / 3.221),
+                     "traffic_note": "scaled from the 2^27-parameter capture in profiles/sgd_multi_tensor_kernel_c5.md",
                      "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650",
                      "frac_of_nominal_8000": achieved / 8000.0},
     }

@@ -84,6 +84,9 @@ LINEAR_SHAPES = [
     (32, 784, 100),     # C1 layer 1 (split-K forward)
     (32, 100, 10),      # C1 head
     (64, 100, 100),
+    (20, 70, 44),       # 32x32 tiles, ragged rows and columns
+    (200, 24, 18),      # 32x32 tiles in dW (18 rows) and dX (24 columns), 64x64 nowhere
+    (500, 2000, 16),    # 32x32 tiles with split K: forward (16 columns) and dW + db (16 rows)
     (257, 130, 66),     # ragged in every dimension, 64x64 tiles
     (4096, 784, 100),   # C2 layer 1 (split-K dW)
     (2048, 1024, 2048), # 128x128 tiles, >= 148 of them
