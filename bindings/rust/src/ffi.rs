@@ -112,6 +112,10 @@ extern "C" {
     pub fn rst_dataset_gather(d: *mut rst_dataset, indices: *const i64, batch: i64, x: *mut rst_tensor,
                               t: *mut rst_tensor) -> c_int;
 
+    pub fn rst_dataset_index_stage(d: *mut rst_dataset, batch: i64, host_indices: *mut *mut i64) -> c_int;
+    pub fn rst_dataset_gather_staged(d: *mut rst_dataset, batch: i64, x: *mut rst_tensor,
+                                     t: *mut rst_tensor) -> c_int;
+
     // data-parallel gradient exchange
     pub fn rst_comm_get_id(id_bytes: *mut c_void) -> c_int;
     pub fn rst_comm_create(ctx: *mut rst_ctx, id_bytes: *const c_void, rank: c_int, world: c_int,

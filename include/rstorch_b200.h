@@ -253,6 +253,18 @@ int rst_dataset_destroy(rst_dataset* d);
 int rst_dataset_len(const rst_dataset* d, int64_t* n);
 int rst_dataset_gather(rst_dataset* d, const int64_t* indices, int64_t batch, rst_tensor* X,
                        rst_tensor* T);
+/* The same batch transform for a step that is replayed as a CUDA graph.
+ * rst_dataset_index_stage hands out a pinned host buffer of at least `batch` indices
+ * that belongs to the dataset (the same buffer on every call until a larger batch is
+ * asked for; ask for it before capturing).  rst_dataset_gather_staged queues the copy
+ * of its first `batch` entries to the device and the gather kernel; it reads no index
+ * on the host, so it may be captured, and every replay gathers whatever the buffer
+ * holds at that time.  The caller writes the next batch's indices only after the
+ * previous replay has consumed them (e.g. after rst_xent_result of that step).  The
+ * kernel checks the indices itself: a row whose index is outside the dataset is
+ * filled with NaN, and the next rst_ctx_check_device returns RST_ERR_INVALID_ARG. */
+int rst_dataset_index_stage(rst_dataset* d, int64_t batch, int64_t** host_indices);
+int rst_dataset_gather_staged(rst_dataset* d, int64_t batch, rst_tensor* X, rst_tensor* T);
 
 /* ---- data-parallel gradient exchange (no counterpart in the reference, which
  * is single-threaded; required to shard the batch over the GPUs of one box) --

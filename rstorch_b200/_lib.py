@@ -89,6 +89,8 @@ _SIGNATURES = {
     "rst_dataset_destroy": [P],
     "rst_dataset_len": [P, C.POINTER(I64)],
     "rst_dataset_gather": [P, C.POINTER(I64), I64, P, P],
+    "rst_dataset_index_stage": [P, I64, C.POINTER(C.POINTER(I64))],
+    "rst_dataset_gather_staged": [P, I64, P, P],
     "rst_comm_get_id": [P],
     "rst_comm_create": [P, P, C.c_int, C.c_int, PP],
     "rst_comm_destroy": [P],

@@ -24,7 +24,7 @@ constexpr int kXentSlots = 64;
 constexpr int kNumSMsFallback = 148;
 
 // Device status word indices (written by kernels, read by rst_ctx_check_device).
-enum DeviceStatus : int { kDevOk = 0, kDevBarrierTimeout = 1 };
+enum DeviceStatus : int { kDevOk = 0, kDevBarrierTimeout = 1, kDevBadIndex = 2 };
 
 // ---------------------------------------------------------------------------
 // Caching allocator: size-bucketed free lists over cudaMalloc.  All tensors of

@@ -24,12 +24,26 @@ constexpr int kIndexSlots = 4;
 __global__ void __launch_bounds__(kGatherThreads)
 gather_normalize_onehot_kernel(const unsigned char* __restrict__ images, const unsigned char* __restrict__ labels,
                                const long long* __restrict__ indices, long long batch, int features, int classes,
-                               double* __restrict__ X, double* __restrict__ T) {
+                               double* __restrict__ X, double* __restrict__ T, long long n_samples,
+                               int* __restrict__ status) {
+    grid_dependency_release();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const long long warp_global = (long long)blockIdx.x * (kGatherThreads / 32) + (threadIdx.x >> 5);
     const long long warp_stride = (long long)gridDim.x * (kGatherThreads / 32);
     for (long long b = warp_global; b < batch; b += warp_stride) {
         const long long idx = indices[b];
+        if (idx < 0 || idx >= n_samples) {
+            // Indices of a replayed graph cannot be checked on the host: flag the batch row,
+            // make it unmistakable, touch nothing outside the dataset.
+            if (lane == 0) {
+                atomicExch(status, kDevBadIndex);
+                atomicExch(status + 1, (int)b);
+            }
+            for (int e = lane; e < features; e += 32) X[b * features + e] = __longlong_as_double(0x7ff8000000000000LL);
+            for (int c = lane; c < classes; c += 32) T[b * classes + c] = 0.0;
+            continue;
+        }
         const unsigned char* src = images + idx * features;
         // pass 1: min and max of the sample by the ordering of u8 (utils.rs:11-12)
         unsigned int lo = 255u, hi = 0u;
@@ -68,6 +82,10 @@ struct rst_dataset {
     long long idx_cap;
     int next_slot;
     bool slot_used[kIndexSlots];
+    // one more pair of index buffers that the caller fills itself (rst_dataset_index_stage)
+    long long* h_stage;
+    long long* d_stage;
+    long long stage_cap;
 };
 
 extern "C" int rst_dataset_destroy(rst_dataset* d);
@@ -88,6 +106,7 @@ extern "C" int rst_dataset_create_u8(rst_ctx* c, const unsigned char* images, co
     rst_dataset* d = new rst_dataset();
     d->ctx = c; d->n = n; d->features = (int)features; d->classes = (int)classes;
     d->d_images = nullptr; d->d_labels = nullptr; d->idx_cap = 0; d->next_slot = 0;
+    d->h_stage = nullptr; d->d_stage = nullptr; d->stage_cap = 0;
     for (int s = 0; s < kIndexSlots; ++s) { d->h_idx[s] = nullptr; d->d_idx[s] = nullptr; d->idx_free[s] = nullptr; d->slot_used[s] = false; }
     bool okay = cudaMalloc((void**)&d->d_images, (size_t)n * features) == cudaSuccess &&
                 cudaMalloc((void**)&d->d_labels, (size_t)n) == cudaSuccess &&
@@ -115,10 +134,40 @@ extern "C" int rst_dataset_destroy(rst_dataset* d) {
         if (d->d_idx[s]) cudaFree(d->d_idx[s]);
         if (d->idx_free[s]) cudaEventDestroy(d->idx_free[s]);
     }
+    if (d->h_stage) cudaFreeHost(d->h_stage);
+    if (d->d_stage) cudaFree(d->d_stage);
     cudaGetLastError();
     delete d;
     return RST_OK;
 }
+
+namespace {
+
+int check_batch_tensors(rst_dataset* d, int64_t batch, rst_tensor* X, rst_tensor* T) {
+    rst_ctx* c = d->ctx;
+    RST_TRY(check_tensor(c, X, "X"));
+    RST_TRY(check_tensor(c, T, "T"));
+    if (batch <= 0) return fail(c, RST_ERR_INVALID_ARG, "empty batch");
+    if (X->rows != batch || X->cols != d->features || T->rows != batch || T->cols != d->classes)
+        return fail(c, RST_ERR_SHAPE, "gather of %lld samples into X (%lld,%lld), T (%lld,%lld); dataset has %d features, %d classes",
+                    (long long)batch, (long long)X->rows, (long long)X->cols, (long long)T->rows, (long long)T->cols,
+                    d->features, d->classes);
+    return RST_OK;
+}
+
+int launch_gather(rst_dataset* d, const long long* d_indices, int64_t batch, rst_tensor* X, rst_tensor* T) {
+    rst_ctx* c = d->ctx;
+    ProfScope prof(c, "gather");
+    long long blocks = (batch + kGatherThreads / 32 - 1) / (kGatherThreads / 32);
+    long long cap = (long long)c->num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    launch_step_kernel(c, c->compute, gather_normalize_onehot_kernel, dim3((unsigned)blocks), dim3(kGatherThreads), 0,
+                       d->d_images, d->d_labels, d_indices, (long long)batch, d->features, d->classes, X->data,
+                       T->data, d->n, c->d_status);
+    return after_launch(c, "gather_normalize_onehot_kernel");
+}
+
+}  // namespace
 
 extern "C" int rst_dataset_len(const rst_dataset* d, int64_t* n) {
     if (!d || !n) return fail(nullptr, RST_ERR_INVALID_ARG, "bad argument");
@@ -130,13 +179,8 @@ extern "C" int rst_dataset_gather(rst_dataset* d, const int64_t* indices, int64_
                                   rst_tensor* T) {
     if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
     rst_ctx* c = d->ctx;
-    RST_TRY(check_tensor(c, X, "X"));
-    RST_TRY(check_tensor(c, T, "T"));
-    if (batch <= 0 || !indices) return fail(c, RST_ERR_INVALID_ARG, "empty batch");
-    if (X->rows != batch || X->cols != d->features || T->rows != batch || T->cols != d->classes)
-        return fail(c, RST_ERR_SHAPE, "gather of %lld samples into X (%lld,%lld), T (%lld,%lld); dataset has %d features, %d classes",
-                    (long long)batch, (long long)X->rows, (long long)X->cols, (long long)T->rows, (long long)T->cols,
-                    d->features, d->classes);
+    if (!indices) return fail(c, RST_ERR_INVALID_ARG, "empty batch");
+    RST_TRY(check_batch_tensors(d, batch, X, T));
     if (c->capturing) return fail(c, RST_ERR_STATE, "gather during graph capture");
     // `dataset.get(index)?` ends the reference's epoch on a missing sample (data_loader.rs:197)
     for (int64_t i = 0; i < batch; ++i)
@@ -164,16 +208,45 @@ extern "C" int rst_dataset_gather(rst_dataset* d, const int64_t* indices, int64_
     for (int64_t i = 0; i < batch; ++i) d->h_idx[s][i] = indices[i];
     RST_CUDA(c, cudaMemcpyAsync(d->d_idx[s], d->h_idx[s], (size_t)batch * sizeof(long long), cudaMemcpyHostToDevice,
                                 c->compute));
-    {
-        ProfScope prof(c, "gather");
-        long long blocks = (batch + kGatherThreads / 32 - 1) / (kGatherThreads / 32);
-        long long cap = (long long)c->num_sms * 8;
-        if (blocks > cap) blocks = cap;
-        gather_normalize_onehot_kernel<<<(int)blocks, kGatherThreads, 0, c->compute>>>(
-            d->d_images, d->d_labels, d->d_idx[s], batch, d->features, d->classes, X->data, T->data);
-        RST_TRY(after_launch(c, "gather_normalize_onehot_kernel"));
-    }
+    RST_TRY(launch_gather(d, d->d_idx[s], batch, X, T));
     RST_CUDA(c, cudaEventRecord(d->idx_free[s], c->compute));
     d->slot_used[s] = true;
     return RST_OK;
+}
+
+// The caller-filled variant: the indices live in a pinned buffer that belongs to the dataset
+// and that the caller writes directly.  Nothing here looks at their values on the host, so
+// the copy and the kernel can be captured into a CUDA graph and replayed with other
+// indices in the buffer; the kernel checks every index against the dataset size itself.
+extern "C" int rst_dataset_index_stage(rst_dataset* d, int64_t batch, int64_t** host_indices) {
+    if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
+    rst_ctx* c = d->ctx;
+    if (batch <= 0 || !host_indices) return fail(c, RST_ERR_INVALID_ARG, "bad index stage arguments");
+    if (batch > d->stage_cap) {
+        if (c->capturing) return fail(c, RST_ERR_STATE, "the index stage cannot grow during graph capture");
+        RST_CUDA(c, cudaStreamSynchronize(c->compute));
+        if (d->h_stage) cudaFreeHost(d->h_stage);
+        if (d->d_stage) cudaFree(d->d_stage);
+        d->h_stage = nullptr; d->d_stage = nullptr; d->stage_cap = 0;
+        if (cudaMallocHost((void**)&d->h_stage, (size_t)batch * sizeof(long long)) != cudaSuccess ||
+            cudaMalloc((void**)&d->d_stage, (size_t)batch * sizeof(long long)) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(c, RST_ERR_OOM, "cannot allocate the index stage for %lld samples", (long long)batch);
+        }
+        d->stage_cap = batch;
+    }
+    *host_indices = reinterpret_cast<int64_t*>(d->h_stage);
+    return RST_OK;
+}
+
+extern "C" int rst_dataset_gather_staged(rst_dataset* d, int64_t batch, rst_tensor* X, rst_tensor* T) {
+    if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
+    rst_ctx* c = d->ctx;
+    RST_TRY(check_batch_tensors(d, batch, X, T));
+    if (batch > d->stage_cap)
+        return fail(c, RST_ERR_STATE, "gather of %lld staged indices, but the index stage holds %lld",
+                    (long long)batch, (long long)d->stage_cap);
+    RST_CUDA(c, cudaMemcpyAsync(d->d_stage, d->h_stage, (size_t)batch * sizeof(long long), cudaMemcpyHostToDevice,
+                                c->compute));
+    return launch_gather(d, d->d_stage, batch, X, T);
 }

@@ -333,6 +333,10 @@ extern "C" int rst_ctx_check_device(rst_ctx* c) {
         RST_CUDA(c, cudaMemsetAsync(c->d_status, 0, 4 * sizeof(int), c->compute));
         // a kernel that gave up may have left the election counter half-counted
         RST_CUDA(c, cudaMemsetAsync(c->xent_counter, 0, 4 * sizeof(unsigned int), c->compute));
+        if (code == kDevBadIndex)
+            return fail(c, RST_ERR_INVALID_ARG,
+                        "a staged gather read a sample index outside the dataset (batch row %d); that row "
+                        "of the batch is NaN", where);
         return fail(c, RST_ERR_DEVICE_TIMEOUT,
                     "a kernel gave up a bounded wait (code %d, site %d); its output is invalid",
                     code, where);

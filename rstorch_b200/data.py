@@ -56,6 +56,18 @@ class DeviceDataset:
         self.ctx._check(self.ctx._lib.rst_dataset_gather(self.handle, idx.ctypes.data_as(C.POINTER(C.c_int64)),
                                                          len(idx), X.handle, T.handle))
 
+    def index_stage(self, batch: int) -> np.ndarray:
+        """The dataset's pinned index buffer as an int64 array of `batch` entries; write the
+        sample indices of the next batch into it and call `gather_staged`."""
+        p = C.POINTER(C.c_int64)()
+        self.ctx._check(self.ctx._lib.rst_dataset_index_stage(self.handle, int(batch), C.byref(p)))
+        return np.ctypeslib.as_array(p, shape=(int(batch),))
+
+    def gather_staged(self, batch: int, X: Tensor, T: Tensor) -> None:
+        """Builds the batch of the indices currently in the index stage.  May be captured
+        into a graph; each replay uses the indices the stage holds at that moment."""
+        self.ctx._check(self.ctx._lib.rst_dataset_gather_staged(self.handle, int(batch), X.handle, T.handle))
+
     def close(self) -> None:
         if self.handle is not None and self.handle.value and self.ctx.handle.value:
             self.ctx._lib.rst_dataset_destroy(self.handle)

@@ -113,3 +113,51 @@ def test_idx_files_to_device_batches(ctx, tmp_path):
         want_x, want_t = on.iter_array_batch(images, labels, np.arange(k * 32, k * 32 + 32), 10)
         assert np.array_equal(x.numpy(), want_x) and np.array_equal(t.numpy(), want_t)
     assert k == 2
+
+
+def test_staged_gather_eager_and_replayed(ctx):
+    """The caller-filled index stage: same batches as `gather`, and a captured graph picks
+    up the indices that are in the stage when it is replayed."""
+    images, labels = synth.mnist_like_u8(4, 0, 200, side=6, classes=5)
+    ds = rt.DeviceDataset(ctx, images, labels, 5)
+    X, T = ctx.empty(48, 36), ctx.empty(48, 5)
+    stage = ds.index_stage(48)
+    assert stage.dtype == np.int64 and stage.shape == (48,)
+    rng = np.random.default_rng(1)
+    idx = rng.permutation(200)[:48]
+    stage[:] = idx
+    ds.gather_staged(48, X, T)
+    want_x, want_t = on.iter_array_batch(images, labels, idx, 5)
+    assert np.array_equal(X.numpy(), want_x, equal_nan=True) and np.array_equal(T.numpy(), want_t)
+    assert ds.index_stage(48).ctypes.data == stage.ctypes.data          # the same buffer until it must grow
+
+    with ctx.capture() as cap:
+        ds.gather_staged(48, X, T)
+    for seed in (2, 3, 4):
+        idx = np.random.default_rng(seed).integers(0, 200, size=48)
+        stage[:] = idx
+        cap.graph.launch()
+        want_x, want_t = on.iter_array_batch(images, labels, idx, 5)
+        assert np.array_equal(X.numpy(), want_x, equal_nan=True) and np.array_equal(T.numpy(), want_t)
+    ctx.check_device()
+
+    # an index outside the dataset cannot be seen on the host: the kernel flags it
+    stage[:] = np.arange(48)
+    stage[5] = 200
+    cap.graph.launch()
+    with pytest.raises(rt.RstError) as e:
+        ctx.check_device()
+    assert e.value.status == _lib.RST_ERR_INVALID_ARG and "batch row 5" in str(e.value)
+    x = X.numpy()
+    assert np.isnan(x[5]).all() and np.array_equal(T.numpy()[5], np.zeros(5))
+    assert np.array_equal(x[6], on.iter_array_batch(images, labels, np.array([6]), 5)[0][0], equal_nan=True)
+    ctx.check_device()                                                   # the flag was cleared
+
+    # shape and capacity errors
+    with pytest.raises(rt.RstError) as e:
+        ds.gather_staged(64, ctx.empty(64, 36), ctx.empty(64, 5))
+    assert e.value.status == _lib.RST_ERR_STATE
+    with pytest.raises(rt.RstError) as e:
+        ds.gather_staged(48, ctx.empty(48, 35), T)
+    assert e.value.status == _lib.RST_ERR_SHAPE
+    ds.close()
