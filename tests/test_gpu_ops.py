@@ -90,6 +90,7 @@ LINEAR_SHAPES = [
     (257, 130, 66),     # ragged in every dimension, 64x64 tiles
     (4096, 784, 100),   # C2 layer 1 (split-K dW)
     (2048, 1024, 2048), # 128x128 tiles, >= 148 of them
+    (2048, 2048, 2048), # 256 large tiles = 1.73 waves: split K four ways in all three products
     (1920, 272, 1288),  # 128x128 tiles with ragged edges in M, N and K
 ]
 
