@@ -16,6 +16,7 @@
 // per block, written as one partial per block, and the last block to finish
 // adds the partials in index order, so the result does not depend on block
 // scheduling.  Algorithmic traffic: 24 B per logit (read x, read t, write g).
+#include <algorithm>
 #include <cfloat>
 
 #include "common.h"
@@ -244,7 +245,119 @@ xent_rows_kernel(const double* __restrict__ logits, const double* __restrict__ t
     if (MODE == 0) finish_block(loss_acc, correct_acc, nan_acc, partials, counter, slot, (double)rows);
 }
 
-// Rows wider than 1024 columns: one warp per row, three sweeps over the row
+// Rows of 129 to 2048 columns: one CTA per row, EPT elements per thread (column =
+// thread + j*256).  A warp per row would need 32 to 64 doubles per lane for x and as many
+// for t, which leaves one CTA of 8 warps per SM at over 200 registers, far too few warps
+// to cover the latency of the f64 exp and division chains (measured: 19 % of the HBM
+// bandwidth on 16384 x 1000).  Here a thread holds at most 2 x 8 doubles, eight CTAs fit an
+// SM, and a row costs two block-wide reductions: (max, NaN flag, both arg-maxima) and the
+// sum of the exponentials.  The loss terms stay per thread across all rows of the CTA and
+// are reduced once, in a fixed order, at the end.
+template <int EPT, int MODE>
+__global__ void __launch_bounds__(kXentThreads)
+xent_block_kernel(const double* __restrict__ logits, const double* __restrict__ truth,
+                  double* __restrict__ out, int64_t rows, int cols, BlockPartial* partials,
+                  unsigned int* counter, ResultSlot* slot) {
+    grid_dependency_release();
+    grid_dependency_wait();
+    __shared__ double sh_max[kWarps], sh_sum[kWarps];
+    __shared__ double sh_xv[kWarps], sh_tv[kWarps];
+    __shared__ int sh_xi[kWarps], sh_ti[kWarps], sh_flags[kWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    double loss_acc = 0.0, correct_acc = 0.0, nan_acc = 0.0;
+
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const double* xr = logits + row * cols;
+        const double* tr = MODE == 0 ? truth + row * cols : nullptr;
+        double x[EPT], t[EPT];
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int col = tid + j * kXentThreads;
+            x[j] = col < cols ? xr[col] : 0.0;
+            t[j] = (MODE == 0 && col < cols) ? tr[col] : 0.0;
+        }
+        // first block-wide reduction: maximum (folded from the most negative finite value like
+        // the reference), NaN flag, arg-maxima of x and t with the fold's tie and NaN rules
+        double m = -DBL_MAX;
+        int flags = 0;                       // 1: a NaN logit, 2: x[0] is NaN, 4: t[0] is NaN
+        ArgMax bx{-INFINITY, 0x7fffffff}, bt{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int col = tid + j * kXentThreads;
+            if (col < cols) {
+                const double v = x[j];
+                if (v != v) flags |= (col == 0) ? 3 : 1;
+                m = v > m ? v : m;
+                if (MODE == 0) {
+                    bx = pick(bx, ArgMax{v != v ? -INFINITY : v, col});
+                    const double w = t[j];
+                    if (w != w && col == 0) flags |= 4;
+                    bt = pick(bt, ArgMax{w != w ? -INFINITY : w, col});
+                }
+            }
+        }
+        m = group_max<32>(m);
+        flags = group_or<32>(flags);
+        if (MODE == 0) { bx = group_argmax<32>(bx); bt = group_argmax<32>(bt); }
+        if (lane == 0) {
+            sh_max[warp] = m; sh_flags[warp] = flags;
+            sh_xv[warp] = bx.v; sh_xi[warp] = bx.i; sh_tv[warp] = bt.v; sh_ti[warp] = bt.i;
+        }
+        __syncthreads();
+        m = sh_max[0]; flags = sh_flags[0];
+        bx = ArgMax{sh_xv[0], sh_xi[0]}; bt = ArgMax{sh_tv[0], sh_ti[0]};
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) {
+            m = sh_max[w] > m ? sh_max[w] : m;
+            flags |= sh_flags[w];
+            if (MODE == 0) {
+                bx = pick(bx, ArgMax{sh_xv[w], sh_xi[w]});
+                bt = pick(bt, ArgMax{sh_tv[w], sh_ti[w]});
+            }
+        }
+        // second: sum of the exponentials, added in warp order by every thread alike
+        double s = 0.0;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int col = tid + j * kXentThreads;
+            if (col < cols) {
+                x[j] = exp(x[j] - m);
+                s += x[j];
+            }
+        }
+        s = group_sum<32>(s);
+        if (lane == 0) sh_sum[warp] = s;
+        __syncthreads();
+        s = sh_sum[0];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) s += sh_sum[w];
+
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int col = tid + j * kXentThreads;
+            if (col < cols) {
+                const double p = x[j] / s;
+                if (MODE == 0) {
+                    loss_acc += loss_term(t[j], p);
+                    if (out) out[row * cols + col] = p - t[j];
+                } else {
+                    out[row * cols + col] = p;
+                }
+            }
+        }
+        if (MODE == 0 && tid == 0) {
+            const int pred_arg = (flags & 2) ? 0 : bx.i, truth_arg = (flags & 4) ? 0 : bt.i;
+            correct_acc += (pred_arg == truth_arg) ? 1.0 : 0.0;
+            nan_acc += (flags & 1) ? 1.0 : 0.0;
+        }
+        // No barrier needed before the next row: a warp can overwrite sh_max and its
+        // companions only after the second barrier of this row, which every thread reaches
+        // after its reads of them, and sh_sum only after the first barrier of the next row.
+    }
+    if (MODE == 0) finish_block(loss_acc, correct_acc, nan_acc, partials, counter, slot, (double)rows);
+}
+
+// Rows wider than 2048 columns: one warp per row, three sweeps over the row
 // (it stays in L1/L2 between them).
 template <int MODE>
 __global__ void __launch_bounds__(kXentThreads)
@@ -375,15 +488,21 @@ int dispatch_rows(rst_ctx* ctx, const double* logits, const double* truth, doubl
     launch_step_kernel(ctx, st, xent_rows_kernel<LPR, EPL, MODE>,                              \
                        dim3((unsigned)xent_grid(ctx, rows, 32 / LPR)), dim3(kXentThreads), 0, \
                        logits, truth, out, rows, c, partials, counter, d_slot)
+#define XENT_BLOCK_CASE(EPT)                                                                          \
+    launch_step_kernel(ctx, st, xent_block_kernel<EPT, MODE>,                                         \
+                       dim3((unsigned)std::min<int64_t>(rows, max_grid)), dim3(kXentThreads), 0,      \
+                       logits, truth, out, rows, c, partials, counter, d_slot)
     if (cols <= 16) XENT_CASE(4, 4);
     else if (cols <= 32) XENT_CASE(8, 4);
     else if (cols <= 128) XENT_CASE(32, 4);
-    else if (cols <= 512) XENT_CASE(32, 16);
-    else if (cols <= 1024) XENT_CASE(32, 32);
+    else if (cols <= 512) XENT_BLOCK_CASE(2);
+    else if (cols <= 1024) XENT_BLOCK_CASE(4);
+    else if (cols <= 2048) XENT_BLOCK_CASE(8);
     else
         xent_wide_kernel<MODE><<<xent_grid(ctx, rows, 1), kXentThreads, 0, st>>>(
             logits, truth, out, rows, c, partials, counter, d_slot);
 #undef XENT_CASE
+#undef XENT_BLOCK_CASE
     return after_launch(ctx, MODE == 0 ? "xent_rows_kernel" : "softmax_rows_kernel");
 }
 

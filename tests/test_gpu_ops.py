@@ -201,7 +201,8 @@ def test_relu_parity(ctx, oc, shape):
 
 # ---- softmax / cross-entropy / accuracy ---------------------------------------------------
 @pytest.mark.parametrize("rows,cols", [(1, 1), (5, 2), (32, 10), (4096, 10), (33, 17), (100, 32), (64, 100),
-                                       (31, 500), (256, 1000), (8, 1024), (5, 1500)])
+                                       (31, 500), (256, 1000), (8, 1024), (5, 1500), (3000, 1000), (40, 2048),
+                                       (7, 2049)])
 def test_xent_parity(ctx, oc, rows, cols):
     rng = np.random.default_rng(rows * 31 + cols)
     x = rng.standard_normal((rows, cols)) * 4
@@ -238,13 +239,37 @@ def test_xent_soft_labels_and_underflow(ctx, oc):
     assert np.isnan(rt.CrossEntropyLoss().forward(ctx.tensor(x2), ctx.tensor(t2)))
 
 
-def test_xent_nan_logit_is_an_error_like_the_reference_panic(ctx):
-    x = np.zeros((4, 10))
+@pytest.mark.parametrize("cols", [10, 1000])
+def test_xent_nan_logit_is_an_error_like_the_reference_panic(ctx, cols):
+    x = np.zeros((4, cols))
     x[2, 3] = np.nan
-    t = np.eye(10)[[0, 1, 2, 3]]
+    t = np.eye(cols)[[0, 1, 2, 3]]
     with pytest.raises(rt.RstError) as e:
         rt.CrossEntropyLoss().forward(ctx.tensor(x), ctx.tensor(t))
     assert e.value.status == _lib.RST_ERR_NAN
+
+
+def test_xent_wide_rows_soft_labels_ties_and_nan_targets(ctx, oc):
+    """The one-CTA-per-row kernel (129 to 2048 classes): soft labels, a tie across two warps'
+    columns, a NaN in column 0 of the targets (argmax answers 0, as the fold does)."""
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((9, 700)) * 3
+    t = rng.random((9, 700))
+    t /= t.sum(axis=1, keepdims=True)
+    x[1, 40] = x[1, 650] = x[1].max() + 2.0              # first of two equal maxima wins
+    t[2, 5] = t[2, 300] = 0.9
+    t[3, 0] = np.nan
+    lf = rt.CrossEntropyLoss()
+    xd, td = ctx.tensor(x), ctx.tensor(t)
+    loss = lf.forward(xd, td)
+    want, p, _ = oc.xent_forward(x, t)
+    assert np.isnan(loss) and np.isnan(want)             # the NaN target poisons the whole-matrix sum
+    got = lf.backward().numpy()
+    ref = oc.xent_backward(p, t)
+    ok = ~np.isnan(ref)
+    assert np.array_equal(np.isnan(got), np.isnan(ref)) and rel_err(got[ok], ref[ok]) < REL_TOL
+    assert lf.last_accuracy == oc.accuracy(x, t)
+    assert np.array_equal(rt.argmax(td), oc.argmax(t)) and rt.argmax(xd)[1] == 40
 
 
 def test_argmax_first_maximum_wins(ctx, oc):
