@@ -25,7 +25,9 @@
 //! }
 //! ```
 pub mod data;
+pub mod dataset;
 pub mod ffi;
+pub mod graph;
 pub mod loss;
 pub mod module;
 pub mod optim;
@@ -33,6 +35,8 @@ pub mod parallel;
 pub mod tensor;
 pub mod utils;
 
+pub use dataset::DeviceDataset;
+pub use graph::Graph;
 pub use loss::CrossEntropyLoss;
 pub use module::{Identity, Linear, ReLU, Sequential, Softmax};
 pub use optim::SGD;
