@@ -16,6 +16,7 @@
 // becomes a cheap copy of the handle here).  Header only; link with -lrstorch_b200.
 #pragma once
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <functional>
@@ -165,6 +166,35 @@ public:
         return p;
     }
     Tensor prev_input;   // any tensor with the sign pattern of the pre-activation
+};
+
+// Softmax as a layer (activation/softmax.rs:5-34, 55-78).  The backward is the reference's, kept
+// as written: Jacobian -(Oᵀ·O) over the whole batch with the diagonal replaced by s(1-s),
+// applied as gradient · jacobian.
+class Softmax : public Module {
+public:
+    explicit Softmax(size_t axis = 1) : axis_(axis) {
+        if (axis > 1) throw Panic(RST_ERR_INVALID_ARG, "axis out of range for a 2-D array");
+    }
+    static Softmax with_axis(size_t axis) { return Softmax(axis); }
+    Tensor forward(Tensor input) override {
+        Tensor out = Tensor::like(input, input.nrows(), input.ncols());
+        check(input.ctx(), axis_ == 1 ? rst_softmax(input.ctx(), input.handle(), out.handle())
+                                      : rst_softmax_axis0(input.ctx(), input.handle(), out.handle()));
+        output_ = out;
+        return out;
+    }
+    Tensor backward(Tensor gradient) override {
+        if (!output_) throw Panic(RST_ERR_STATE, "Softmax::backward without a preceding forward (softmax.rs:63 unwrap)");
+        Tensor output = output_;
+        output_ = Tensor();
+        Tensor dx = Tensor::like(gradient, gradient.nrows(), output.ncols());
+        check(gradient.ctx(), rst_softmax_backward(gradient.ctx(), output.handle(), gradient.handle(), dx.handle()));
+        return dx;
+    }
+private:
+    size_t axis_;
+    Tensor output_;
 };
 
 class Linear : public Module {     // module/linear.rs
@@ -441,6 +471,55 @@ private:
     int64_t n_, f_, c_, b_;
     int slots_;
     rst_stager* stager_ = nullptr;
+};
+
+// A u8 dataset resident in HBM (the MNIST item type, data/dataset/hub/mnist.rs:181-194) with
+// the README transform `(flatten(normalize_zero_one(x)), one_hot(y, classes))` applied by the
+// kernel that builds a batch (README.md:44, utils.rs:5-42, data_loader.rs:192-207).
+class DeviceDataset {
+public:
+    DeviceDataset(Context& ctx, const std::vector<unsigned char>& images, const std::vector<unsigned char>& labels,
+                  int64_t features, int64_t classes)
+        : ctx_(ctx.handle()), n_((int64_t)labels.size()), f_(features), c_(classes) {
+        if ((int64_t)images.size() != n_ * f_) throw Panic(RST_ERR_SHAPE, "images and labels differ in length");
+        check(ctx_, rst_dataset_create_u8(ctx_, images.data(), labels.data(), n_, f_, c_, &h_));
+    }
+    ~DeviceDataset() { if (h_) rst_dataset_destroy(h_); }
+    DeviceDataset(const DeviceDataset&) = delete;
+    size_t len() const { return (size_t)n_; }
+    // The batch of the given sample indices: X (n, features), T (n, classes).
+    std::pair<Tensor, Tensor> gather(Context& ctx, const std::vector<int64_t>& indices) {
+        Tensor x(ctx, (int64_t)indices.size(), f_), t(ctx, (int64_t)indices.size(), c_);
+        check(ctx_, rst_dataset_gather(h_, indices.data(), (int64_t)indices.size(), x.handle(), t.handle()));
+        return {x, t};
+    }
+    // The pinned index buffer a replayed step reads its sample indices from.
+    int64_t* index_stage(int64_t batch) {
+        int64_t* p = nullptr;
+        check(ctx_, rst_dataset_index_stage(h_, batch, &p));
+        return p;
+    }
+    // Builds the batch of the staged indices into x, t; reads no index on the host (capturable).
+    void gather_staged(int64_t batch, Tensor& x, Tensor& t) {
+        check(ctx_, rst_dataset_gather_staged(h_, batch, x.handle(), t.handle()));
+    }
+private:
+    rst_ctx* ctx_;
+    int64_t n_, f_, c_;
+    rst_dataset* h_ = nullptr;
+};
+
+// Everything queued between the constructor and end() becomes a CUDA graph; launch() replays it.
+class Graph {
+public:
+    explicit Graph(Context& ctx) : ctx_(ctx.handle()) { check(ctx_, rst_graph_capture_begin(ctx_)); }
+    ~Graph() { if (h_) rst_graph_destroy(h_); }
+    Graph(const Graph&) = delete;
+    void end() { check(ctx_, rst_graph_capture_end(ctx_, &h_)); }
+    void launch() { check(ctx_, rst_graph_launch(h_)); }
+private:
+    rst_ctx* ctx_;
+    rst_graph* h_ = nullptr;
 };
 
 }  // namespace rstorch

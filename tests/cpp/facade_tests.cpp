@@ -102,6 +102,57 @@ static void unit_tests(Context& ctx) {
         EXPECT(threw);
         EXPECT(one_hot(3, 5) == (std::vector<double>{0, 0, 0, 1, 0}));
     }
+    {   // softmax.rs:85-113: rows (axis 1) and columns (axis 0) sum to one; backward known answer
+        Softmax rows;
+        std::vector<double> p = rows.forward(Tensor(ctx, 3, 2, {1.0, 10.0, -3.0, 4.0, 5.0, 6.0})).to_host();
+        for (int r = 0; r < 3; ++r) EXPECT(std::fabs(p[2 * r] + p[2 * r + 1] - 1.0) <= 1e-6);
+        Softmax cols = Softmax::with_axis(0);
+        Tensor data(ctx, 3, 2, {1.0, 2.0, 3.0, 4.0, 5.0, 6.0});
+        std::vector<double> q = cols.forward(data).to_host();
+        EXPECT(std::fabs(q[0] + q[2] + q[4] - 1.0) <= 1e-6 && std::fabs(q[1] + q[3] + q[5] - 1.0) <= 1e-6);
+        Softmax m;
+        m.forward(data);
+        std::vector<double> g = m.backward(Tensor(ctx, 3, 2, std::vector<double>(6, 1.0))).to_host();
+        EXPECT(close_to(g, {-0.41, -1.55, -0.41, -1.55, -0.41, -1.55}, 0.01));
+        bool threw = false;
+        try { Softmax().backward(data); } catch (const Panic&) { threw = true; }
+        EXPECT(threw);
+    }
+    {   // device-resident u8 dataset: README transform in the gather kernel, eager and replayed
+        const int64_t n = 40, f = 6, c = 4, b = 8;
+        std::vector<unsigned char> images((size_t)(n * f)), labels((size_t)n);
+        for (int64_t i = 0; i < n; ++i) {
+            labels[(size_t)i] = (unsigned char)(i % c);
+            for (int64_t e = 0; e < f; ++e) images[(size_t)(i * f + e)] = (unsigned char)((i * 37 + e * 11) % 251);
+        }
+        DeviceDataset ds(ctx, images, labels, f, c);
+        EXPECT(ds.len() == 40);
+        auto expect_batch = [&](const std::vector<int64_t>& idx, const std::vector<double>& x, const std::vector<double>& t) {
+            for (size_t r = 0; r < idx.size(); ++r) {
+                const unsigned char* s = &images[(size_t)(idx[r] * f)];
+                double lo = 255, hi = 0;
+                for (int64_t e = 0; e < f; ++e) { lo = std::min<double>(lo, s[e]); hi = std::max<double>(hi, s[e]); }
+                for (int64_t e = 0; e < f; ++e) EXPECT(x[r * (size_t)f + (size_t)e] == (s[e] - lo) / (hi - lo));
+                for (int64_t k = 0; k < c; ++k) EXPECT(t[r * (size_t)c + (size_t)k] == (k == labels[(size_t)idx[r]] ? 1.0 : 0.0));
+            }
+        };
+        std::vector<int64_t> idx = {3, 39, 0, 17, 17, 8, 21, 30};
+        auto [x, t] = ds.gather(ctx, idx);
+        expect_batch(idx, x.to_host(), t.to_host());
+        Tensor xs(ctx, b, f), ts(ctx, b, c);
+        int64_t* stage = ds.index_stage(b);
+        std::copy(idx.begin(), idx.end(), stage);
+        ds.gather_staged(b, xs, ts);
+        expect_batch(idx, xs.to_host(), ts.to_host());
+        Graph g(ctx);
+        ds.gather_staged(b, xs, ts);
+        g.end();
+        std::vector<int64_t> idx2 = {1, 2, 3, 4, 5, 6, 7, 38};
+        std::copy(idx2.begin(), idx2.end(), stage);
+        g.launch();
+        expect_batch(idx2, xs.to_host(), ts.to_host());
+        ctx.check_device();
+    }
 }
 
 template <class T> static void read_vec(std::ifstream& f, std::vector<T>& v, size_t n) {
