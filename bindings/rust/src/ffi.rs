@@ -65,6 +65,11 @@ extern "C" {
                                      x: *const *const rst_tensor, w: *const *const rst_tensor,
                                      relu_mask: *const c_uchar, dw: *const *mut rst_tensor,
                                      db: *const *mut rst_tensor, dx: *const *mut rst_tensor) -> c_int;
+    pub fn rst_linear_backward_t(ctx: *mut rst_ctx, dy: *const rst_tensor, dy_t: *const rst_tensor,
+                                 x: *const rst_tensor, w: *const rst_tensor, relu_mask_src: *const rst_tensor,
+                                 dw: *mut rst_tensor, db: *mut rst_tensor, dx: *mut rst_tensor,
+                                 dx_t: *mut rst_tensor) -> c_int;
+    pub fn rst_transpose(ctx: *mut rst_ctx, src: *const rst_tensor, dst: *mut rst_tensor) -> c_int;
     pub fn rst_bias_grad_noalloc(dy: *const c_double, rows: i64, cols: i64, db: *mut c_double,
                                  stream: *mut c_void) -> c_int;
 

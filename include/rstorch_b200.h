@@ -144,6 +144,19 @@ int rst_linear_backward_chain(rst_ctx* ctx, int n, const rst_tensor* dY, const r
                               const rst_tensor* const* W, const unsigned char* relu_mask,
                               rst_tensor* const* dW, rst_tensor* const* db, rst_tensor* const* dX);
 
+/* rst_linear_backward for a caller that keeps a transposed companion of each gradient
+ * (no counterpart in the reference; a layout optimisation).  dX = dY · W runs fastest
+ * when both operands are stored with the reduction index outermost: W (out, in) is;
+ * dY (B, out) is not, but dY_t (out, B) is.  dY_t may be NULL (then this is
+ * rst_linear_backward).  dX_t (in, B), if given, receives dXᵀ, written by the same
+ * kernel as dX where the shapes allow and by a transpose kernel otherwise, so that the
+ * layer below can be called the same way.  rst_transpose makes the first companion
+ * (of the loss gradient): dst (cols, rows) = srcᵀ. */
+int rst_linear_backward_t(rst_ctx* ctx, const rst_tensor* dY, const rst_tensor* dY_t,
+                          const rst_tensor* X, const rst_tensor* W, const rst_tensor* relu_mask_src,
+                          rst_tensor* dW, rst_tensor* db, rst_tensor* dX, rst_tensor* dX_t);
+int rst_transpose(rst_ctx* ctx, const rst_tensor* src, rst_tensor* dst);
+
 /* Bias gradient without any allocation: db[c] = (Σ_r dY[r,c]) / rows, the same
  * value rst_linear_backward writes to db.  This entry point has no counterpart in
  * the reference; it exists for hosts that cannot call cudaMalloc where they need

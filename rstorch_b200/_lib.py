@@ -65,6 +65,8 @@ _SIGNATURES = {
     "rst_linear_forward": [P, P, P, P, C.c_int, P],
     "rst_linear_backward": [P, P, P, P, P, P, P, P],
     "rst_linear_backward_chain": [P, C.c_int, P, P, P, P, P, P, P],
+    "rst_linear_backward_t": [P, P, P, P, P, P, P, P, P, P],
+    "rst_transpose": [P, P, P],
     "rst_bias_grad_noalloc": [P, I64, I64, P, P],
     "rst_relu_forward": [P, P, P],
     "rst_relu_backward": [P, P, P, P],

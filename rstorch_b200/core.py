@@ -132,12 +132,15 @@ class Context:
 class Tensor:
     """Dense row-major f64 matrix in HBM; the stand-in for `Array2<f64>`."""
 
-    __slots__ = ("ctx", "handle", "rows", "cols", "_base", "_owns")
+    __slots__ = ("ctx", "handle", "rows", "cols", "_base", "_owns", "t")
 
     def __init__(self, ctx: Context, handle, rows: int, cols: int, base: "Tensor | None" = None,
                  owns: bool = True):
         self.ctx, self.handle, self.rows, self.cols, self._base = ctx, handle, rows, cols, base
         self._owns = owns
+        # transposed companion (cols, rows) that a backward pass may attach to a gradient it
+        # has just produced; valid only as long as nothing writes this tensor again
+        self.t: "Tensor | None" = None
 
     @property
     def shape(self) -> tuple[int, int]:
@@ -152,6 +155,7 @@ class Tensor:
         if a.size != self.numel:
             raise ValueError(f"upload of {a.shape} into tensor {self.shape}")
         self.ctx._check(self.ctx._lib.rst_tensor_upload(self.handle, a.ctypes.data_as(C.c_void_p)))
+        self.t = None
         return self
 
     def numpy(self) -> np.ndarray:
@@ -161,6 +165,7 @@ class Tensor:
 
     def fill(self, value: float) -> "Tensor":
         self.ctx._check(self.ctx._lib.rst_tensor_fill(self.handle, float(value)))
+        self.t = None
         return self
 
     def clone(self) -> "Tensor":

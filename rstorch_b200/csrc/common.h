@@ -187,7 +187,11 @@ struct GemmArgs {
     const double* mask_src;   // [M,N]        (kEpiMask)
     double divisor;           // n            (kEpiDivN)
     double* colsum_out;       // optional [M]: Σ_k A(m,k) / divisor when A is M-major (db)
+    double* C_transposed;     // optional [N,M]: a second, transposed copy of C (M-major A with N-major B
+                              // and large tiles only; the caller checks gemm_writes_transposed)
 };
+// Whether launch_gemm would honour C_transposed for this product.
+bool gemm_writes_transposed(const rst_ctx* ctx, const GemmArgs& a);
 // *colsum_done (optional) tells whether colsum_out was produced by the GEMM kernel itself.
 int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done = nullptr);
 // Up to four dW-type products (M-major A, N-major B, 1/n epilogue, column sums) in one
@@ -201,6 +205,7 @@ int launch_relu_forward(rst_ctx* ctx, const double* x, double* y, int64_t n);
 int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, double* dx,
                          int64_t n);
 int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n);
+int launch_transpose(rst_ctx* ctx, const double* src, int64_t rows, int64_t cols, double* dst);
 int launch_softmax_axis0(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols);
 int launch_softmax_jacobian_diag(rst_ctx* ctx, double* J, int64_t n);
 int launch_softmax(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols);

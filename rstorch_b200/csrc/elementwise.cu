@@ -85,6 +85,27 @@ __global__ void __launch_bounds__(kThreads) softmax_jacobian_diag_kernel(double*
     J[j * n + j] = el;
 }
 
+// dst[c][r] = src[r][c] through a padded 32x32 shared tile: reads and writes are both
+// contiguous along their own rows.  256 threads = 32 columns x 8 rows, four row steps.
+__global__ void __launch_bounds__(kThreads) transpose_kernel(const double* __restrict__ src,
+                                                             double* __restrict__ dst, int64_t rows, int64_t cols) {
+    __shared__ double tile[32][33];
+    const int64_t tiles_c = (cols + 31) / 32;
+    const int64_t r0 = (blockIdx.x / tiles_c) * 32, c0 = (blockIdx.x % tiles_c) * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t r = r0 + ty + 8 * j, c = c0 + tx;
+        if (r < rows && c < cols) tile[ty + 8 * j][tx] = src[r * cols + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int64_t c = c0 + ty + 8 * j, r = r0 + tx;
+        if (r < rows && c < cols) dst[c * rows + r] = tile[tx][ty + 8 * j];
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) fill_kernel(double* __restrict__ x, double v, int64_t n) {
     int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -172,6 +193,14 @@ int launch_softmax_jacobian_diag(rst_ctx* ctx, double* J, int64_t n) {
     if (n == 0) return RST_OK;
     softmax_jacobian_diag_kernel<<<(unsigned)((n + kThreads - 1) / kThreads), kThreads, 0, ctx->compute>>>(J, n);
     return after_launch(ctx, "softmax_jacobian_diag_kernel");
+}
+
+int launch_transpose(rst_ctx* ctx, const double* src, int64_t rows, int64_t cols, double* dst) {
+    if (rows == 0 || cols == 0) return RST_OK;
+    const int64_t tiles = ((rows + 31) / 32) * ((cols + 31) / 32);
+    if (tiles > 0x7fffffffLL) return fail(ctx, RST_ERR_UNSUPPORTED, "matrix too large to transpose in one launch");
+    transpose_kernel<<<(unsigned)tiles, kThreads, 0, ctx->compute>>>(src, dst, rows, cols);
+    return after_launch(ctx, "transpose_kernel");
 }
 
 int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n) {

@@ -34,6 +34,7 @@ struct GemmParams {
     const double* mask_src;
     double* splitk_ws;      // [splits][M][N] raw partial sums when splits > 1, then [splits][M] column sums
     double* colsum_out;     // [M]: Σ_k A(m,k) / divisor, fused into the M-major-A kernel (db of Linear::backward)
+    double* Ct;             // [N][M]: optional transposed copy of C (splits == 1, M-major A, N-major B)
     int* status;
     double divisor;
     long long M, N, K;
@@ -122,7 +123,8 @@ struct Cfg {
 // One CTA's share of one product: output tile `tile_index` (in the grouped order below),
 // k range of split `split`.  tmA and tmB must refer to kernel parameters declared
 // __grid_constant__ (the TMA unit reads the descriptors through their address).
-template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM,
+          bool WRITE_T = false>
 __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                           const int tile_index, const int split) {
     using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
@@ -366,12 +368,40 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
                             double v[4] = {acc[mt][nt][2 * h], acc[mt][nt + 1][2 * h], acc[mt][nt][2 * h + 1],
                                            acc[mt][nt + 1][2 * h + 1]};
                             emit_run<4>(p, r, col_of(nt, 0), v, vec_ok);
+                            if (WRITE_T) {    // keep the finished values for the transposed copy below
+                                acc[mt][nt][2 * h] = v[0]; acc[mt][nt + 1][2 * h] = v[1];
+                                acc[mt][nt][2 * h + 1] = v[2]; acc[mt][nt + 1][2 * h + 1] = v[3];
+                            }
                         }
                     }
                     if (FUSE_COLSUM) {
                         if (do_colsum && t == 0) p.colsum_out[r] = asum[mt][h] / p.divisor;
                     }
                 }
+            // Second, transposed copy of the finished tile ([N][M] in memory), for a consumer
+            // that wants this matrix as an M-major operand (the dX product of the next layer
+            // down reads the gradient that way).  A thread holds rows 2g and 2g+1 of a column:
+            // one 16-byte store each.  The host asks for it only when the runs above took the
+            // vector path (N a multiple of 4, M even, aligned bases), so `acc` holds final values.
+            if (WRITE_T) {
+                static_assert(!WRITE_T || (!A_K && !B_K), "the transposed copy is written from the M-/N-major layout");
+                if (p.Ct != nullptr && vec_ok) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const long long r0 = row_of(mt, 0);
+                        if (r0 >= p.M) continue;
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const long long c = col_of(nt, e);
+                                if (c < p.N)
+                                    *reinterpret_cast<double2*>(p.Ct + c * p.M + r0) =
+                                        make_double2(acc[mt][nt][e], acc[mt][nt][2 + e]);
+                            }
+                    }
+                }
+            }
         }
         return;
     }
@@ -399,12 +429,13 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
         }
 }
 
-template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM,
+          bool WRITE_T = false>
 __global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
 gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const GemmParams p) {
-    gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM>(tmA, tmB, p, (int)blockIdx.x,
-                                                                      (int)blockIdx.y);
+    gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM, WRITE_T>(tmA, tmB, p, (int)blockIdx.x,
+                                                                               (int)blockIdx.y);
 }
 
 // Several independent products of one layout in one launch: the dW (and db) products of
@@ -496,10 +527,11 @@ int encode_map(rst_ctx* ctx, CUtensorMap* map, const double* base, long long inn
     return RST_OK;
 }
 
-template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM,
+          bool WRITE_T = false>
 int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
-    auto kernel = gemm_f64_tma_dmma<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM>;
+    auto kernel = gemm_f64_tma_dmma<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM, WRITE_T>;
     static bool attr_set[16] = {false};   // per device
     if (!attr_set[ctx->device & 15]) {
         RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes));
@@ -544,22 +576,31 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
 constexpr int kSmallBM = 64, kSmallBN = 64, kSmallWM = 2, kSmallWN = 4, kSmallStages = 8;
 constexpr int kTinyB = 32;
 
+// A few waves of large tiles with a mostly empty last one (512 tiles on 148 SMs: 3.46 waves,
+// 13 % of the time on a quarter-full GPU): split K two to four ways when that fills the last
+// wave to 95 % and leaves at least 32 k-tiles per split.
+int large_tile_splits(const rst_ctx* ctx, long long tiles_large, long long k_tiles) {
+    auto fill = [&](long long ctas) {
+        const long long waves = (ctas + ctx->num_sms - 1) / ctx->num_sms;
+        return (double)ctas / (double)(waves * ctx->num_sms);
+    };
+    if (tiles_large <= 4LL * ctx->num_sms && fill(tiles_large) < 0.95)
+        for (int s = 2; s <= 4; ++s)
+            if (k_tiles / s >= 32 && fill(tiles_large * s) >= 0.95) return s;
+    return 1;
+}
+
 template <bool A_K, bool B_K>
 int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_done) {
     const long long k_tiles = (a.K + kBK - 1) / kBK;
     const long long tiles_large = ((a.M + 127) / 128) * ((a.N + 127) / 128);
     if (tiles_large >= ctx->num_sms) {
-        // A few waves of large tiles with a mostly empty last one (512 tiles on 148 SMs: 3.46
-        // waves, 13 % of the time on a quarter-full GPU): split K two to four ways when that
-        // fills the last wave to 95 % and leaves at least 32 k-tiles per split.
-        int splits = 1;
-        auto fill = [&](long long ctas) {
-            const long long waves = (ctas + ctx->num_sms - 1) / ctx->num_sms;
-            return (double)ctas / (double)(waves * ctx->num_sms);
-        };
-        if (tiles_large <= 4LL * ctx->num_sms && fill(tiles_large) < 0.95)
-            for (int s = 2; s <= 4; ++s)
-                if (k_tiles / s >= 32 && fill(tiles_large * s) >= 0.95) { splits = s; break; }
+        const int splits = large_tile_splits(ctx, tiles_large, k_tiles);
+        if (!A_K && !B_K) {
+            // the variant that also stores the transposed copy is an instantiation of its own, so
+            // that the dW product keeps its registers
+            if (p.Ct != nullptr) return launch_cfg<128, 128, 2, 4, 6, false, false, false, true>(ctx, a, p, splits);
+        }
         return launch_cfg<128, 128, 2, 4, 6, A_K, B_K, false>(ctx, a, p, splits);
     }
     // Small problems: 64x64 tiles.  CTAs that share an SM share its f64 tensor pipe,
@@ -590,6 +631,18 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
 
 }  // namespace
 
+bool gemm_writes_transposed(const rst_ctx* ctx, const GemmArgs& a) {
+    if (a.a_kmajor || a.b_kmajor || !a.C_transposed) return false;
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.M > 0x7fffff00LL || a.N > 0x7fffff00LL || a.K > 0x7fffff00LL) return false;
+    if ((a.M % 2) || (a.N % 4)) return false;
+    if ((((uintptr_t)a.A | (uintptr_t)a.B | (uintptr_t)a.C_transposed) & 15u) != 0) return false;
+    if ((((uintptr_t)a.C | (uintptr_t)a.mask_src | (uintptr_t)a.bias) & 31u) != 0) return false;
+    if (a.epilogue != kEpiNone && a.epilogue != kEpiMask) return false;
+    const long long tiles_large = ((a.M + 127) / 128) * ((a.N + 127) / 128);
+    const long long k_tiles = (a.K + kBK - 1) / kBK;
+    return tiles_large >= ctx->num_sms && large_tile_splits(ctx, tiles_large, k_tiles) == 1;
+}
+
 int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done) {
     if (colsum_done) *colsum_done = false;
     if (a.M == 0 || a.N == 0) return RST_OK;
@@ -600,6 +653,11 @@ int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done) {
     p.colsum_out = nullptr;
     p.status = ctx->d_status; p.divisor = a.divisor;
     p.M = a.M; p.N = a.N; p.K = a.K; p.epilogue = a.epilogue; p.splits = 1;
+    if (a.C_transposed) {
+        if (!gemm_writes_transposed(ctx, a))
+            return fail(ctx, RST_ERR_UNSUPPORTED, "a transposed copy of C is not available for this product");
+        p.Ct = a.C_transposed;
+    }
 
     // TMA needs 16-byte aligned bases and row pitches: the contiguous extent of
     // each operand must be even.

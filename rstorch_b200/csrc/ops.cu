@@ -133,6 +133,66 @@ extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_t
     return RST_OK;
 }
 
+extern "C" int rst_transpose(rst_ctx* c, const rst_tensor* src, rst_tensor* dst) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_tensor(c, src, "src"));
+    RST_TRY(check_tensor(c, dst, "dst"));
+    if (dst->rows != src->cols || dst->cols != src->rows)
+        return fail(c, RST_ERR_SHAPE, "transpose of (%lld,%lld) into (%lld,%lld)", (long long)src->rows,
+                    (long long)src->cols, (long long)dst->rows, (long long)dst->cols);
+    if (dst->data == src->data) return fail(c, RST_ERR_INVALID_ARG, "transpose in place");
+    return launch_transpose(c, src->data, src->rows, src->cols, dst->data);
+}
+
+// Linear::backward with transposed companions of the gradients.  The dX product is fastest
+// when both of its operands are stored with the reduction index outermost: W [out][in] is,
+// dY [B][out] is not, its transpose [out][B] is.  A caller that holds dYᵀ passes it, and
+// asks for dXᵀ next to dX so that the layer below can do the same.
+extern "C" int rst_linear_backward_t(rst_ctx* c, const rst_tensor* dY, const rst_tensor* dY_t,
+                                     const rst_tensor* X, const rst_tensor* W, const rst_tensor* mask,
+                                     rst_tensor* dW, rst_tensor* db, rst_tensor* dX, rst_tensor* dX_t) {
+    RST_TRY(need_ctx(c));
+    RST_TRY(check_linear_backward(c, dY, X, W, mask, dW, db, dX));
+    if (dY_t) {
+        RST_TRY(check_tensor(c, dY_t, "dY_t"));
+        if (dY_t->rows != dY->cols || dY_t->cols != dY->rows)
+            return fail(c, RST_ERR_SHAPE, "Linear::backward: dY_t is (%lld,%lld), expected (%lld,%lld)",
+                        (long long)dY_t->rows, (long long)dY_t->cols, (long long)dY->cols, (long long)dY->rows);
+    }
+    if (dX_t) {
+        if (!dX) return fail(c, RST_ERR_INVALID_ARG, "dX_t given without dX");
+        RST_TRY(check_tensor(c, dX_t, "dX_t"));
+        if (dX_t->rows != dX->cols || dX_t->cols != dX->rows)
+            return fail(c, RST_ERR_SHAPE, "Linear::backward: dX_t is (%lld,%lld), expected (%lld,%lld)",
+                        (long long)dX_t->rows, (long long)dX_t->cols, (long long)dX->cols, (long long)dX->rows);
+        if (dX_t->data == dX->data || dX_t->data == dY->data || dX_t->data == W->data)
+            return fail(c, RST_ERR_INVALID_ARG, "Linear::backward: dX_t aliases another operand");
+    }
+    RST_TRY(weight_grad(c, dY, X, dW, db));
+    if (!dX) return RST_OK;
+    if (!dY_t) {
+        RST_TRY(input_grad(c, dY, W, mask, dX));
+    } else {
+        GemmArgs gx{};
+        gx.A = dY_t->data; gx.B = W->data; gx.C = dX->data;         // dX[B,in] = (dYᵀ)ᵀ · W
+        gx.M = dY->rows; gx.N = W->cols; gx.K = W->rows;
+        gx.a_kmajor = false; gx.b_kmajor = false;
+        gx.epilogue = mask ? kEpiMask : kEpiNone;
+        gx.mask_src = mask ? mask->data : nullptr;
+        gx.divisor = 1.0;
+        gx.C_transposed = dX_t ? dX_t->data : nullptr;
+        const bool fused_copy = dX_t && gemm_writes_transposed(c, gx);
+        if (!fused_copy) gx.C_transposed = nullptr;
+        {
+            ProfScope prof(c, "gemm_dX");
+            RST_TRY(launch_gemm(c, gx));
+        }
+        if (!dX_t || fused_copy) return RST_OK;
+    }
+    if (dX_t) RST_TRY(launch_transpose(c, dX->data, dX->rows, dX->cols, dX_t->data));
+    return RST_OK;
+}
+
 // Sequential::backward over n Linear layers (src/module/sequential.rs:88-94 folding
 // linear.rs:60-69, with relu.rs:26 for the ReLUs in between).  The dX products form a
 // dependent chain and run first; the dW/db products only read that chain's tensors and

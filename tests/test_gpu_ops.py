@@ -422,3 +422,50 @@ def test_graph_replay_reproduces_the_eager_step(ctx, oc):
     for a, b in zip(eager.parameters(), graphed.parameters()):
         assert np.array_equal(a.parm.numpy(), b.parm.numpy())
     cap.graph.destroy()
+
+
+@pytest.mark.parametrize("B,cin,cout,fused_copy", [
+    (2048, 1280, 640, True),     # 160 large tiles, no split: dX and its transposed copy from one kernel
+    (2048, 2048, 2048, False),   # 256 large tiles split K four ways: separate transpose kernel
+    (96, 64, 40, False),         # small tiles
+    (50, 33, 21, False),         # odd widths: plain-load kernel
+])
+def test_linear_backward_with_transposed_companions(ctx, oc, B, cin, cout, fused_copy):
+    rng = np.random.default_rng(B + cin)
+    X = np.maximum(rng.standard_normal((B, cin)), 0.0)
+    W, dY = rng.standard_normal((cout, cin)) / np.sqrt(cin), rng.standard_normal((B, cout))
+    xd, wd, gd = ctx.tensor(X), ctx.tensor(W), ctx.tensor(dY)
+    gt = ctx.empty(cout, B)
+    ctx._check(ctx._lib.rst_transpose(ctx.handle, gd.handle, gt.handle))
+    assert np.array_equal(gt.numpy(), dY.T)
+    dW, db, dX, dXt = ctx.empty(cout, cin), ctx.empty(1, cout), ctx.empty(B, cin), ctx.empty(cin, B)
+    before = ctx.launch_count()
+    ctx._check(ctx._lib.rst_linear_backward_t(ctx.handle, gd.handle, gt.handle, xd.handle, wd.handle, xd.handle,
+                                              dW.handle, db.handle, dX.handle, dXt.handle))
+    launches = ctx.launch_count() - before
+    want_dW, want_db, want_dX = oc.linear_backward(dY, X, W)
+    want_dX = want_dX * (X > 0.0)
+    assert rel_err(dW.numpy(), want_dW) < REL_TOL and rel_err(db.numpy(), want_db) < REL_TOL
+    assert rel_err(dX.numpy(), want_dX) < REL_TOL
+    assert np.array_equal(dXt.numpy(), dX.numpy().T)                     # the same values, transposed
+    # against the plain entry point: another kernel variant, same sums in another order
+    dW2, db2, dX2 = ctx.empty(cout, cin), ctx.empty(1, cout), ctx.empty(B, cin)
+    before = ctx.launch_count()
+    ctx._check(ctx._lib.rst_linear_backward(ctx.handle, gd.handle, xd.handle, wd.handle, xd.handle,
+                                            dW2.handle, db2.handle, dX2.handle))
+    plain_launches = ctx.launch_count() - before
+    assert rel_err(dX.numpy(), dX2.numpy()) < 1e-13 and np.array_equal(dW.numpy(), dW2.numpy())
+    if fused_copy:
+        assert launches == plain_launches                                # no transpose launch
+    # without the companions the call is rst_linear_backward; dX_t alone is honoured too
+    dX3, dXt3 = ctx.empty(B, cin), ctx.empty(cin, B)
+    ctx._check(ctx._lib.rst_linear_backward_t(ctx.handle, gd.handle, None, xd.handle, wd.handle, xd.handle,
+                                              dW.handle, db.handle, dX3.handle, dXt3.handle))
+    assert np.array_equal(dX3.numpy(), dX2.numpy()) and np.array_equal(dXt3.numpy(), dX2.numpy().T)
+    # shape errors: a companion that is not (cols, rows) of its tensor
+    wrong = ctx.empty(cout + 1, B)
+    assert ctx._lib.rst_linear_backward_t(ctx.handle, gd.handle, wrong.handle, xd.handle, wd.handle, None,
+                                          dW.handle, db.handle, dX.handle, None) == _lib.RST_ERR_SHAPE
+    assert ctx._lib.rst_linear_backward_t(ctx.handle, gd.handle, gt.handle, xd.handle, wd.handle, None,
+                                          dW.handle, db.handle, dX.handle, wrong.handle) == _lib.RST_ERR_SHAPE
+    assert ctx._lib.rst_transpose(ctx.handle, gd.handle, wrong.handle) == _lib.RST_ERR_SHAPE
