@@ -717,7 +717,7 @@ int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped) 
     GroupMaps maps;
     GroupParams gp{};
     gp.count = n;
-    size_t ws_elems = 0;
+    size_t ws_elems = 0, ws_offset[kMaxGroup] = {};
     long long reduce_elems = 0;
     // longest CTAs first: products in decreasing k-tiles per CTA
     int order[kMaxGroup];
@@ -746,7 +746,7 @@ int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped) 
         gp.first_cta[slot] = cta;
         cta += p.tiles_m * p.tiles_n * p.splits;
         if (p.splits > 1) {
-            p.splitk_ws = reinterpret_cast<double*>(ws_elems);      // offset for now, base added below
+            ws_offset[slot] = ws_elems;                              // the base is added once it is known
             ws_elems += (size_t)p.splits * ((size_t)a.M * (size_t)a.N + (size_t)a.M);
             ws_elems = (ws_elems + 1) & ~(size_t)1;                  // keep every region 16-byte aligned
             reduce_elems = std::max(reduce_elems, (long long)(a.M * a.N + (a.colsum_out ? a.M : 0)));
@@ -757,8 +757,7 @@ int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped) 
         RST_TRY(ensure_scratch(ctx, (void**)&ctx->splitk_ws, &ctx->splitk_ws_bytes, ws_elems * sizeof(double),
                                "split-K"));
         for (int slot = 0; slot < n; ++slot)
-            if (gp.p[slot].splits > 1)
-                gp.p[slot].splitk_ws = ctx->splitk_ws + reinterpret_cast<size_t>(gp.p[slot].splitk_ws);
+            if (gp.p[slot].splits > 1) gp.p[slot].splitk_ws = ctx->splitk_ws + ws_offset[slot];
     }
 
     auto kernel = gemm_f64_tma_dmma_grouped<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, false, false, true>;
