@@ -38,6 +38,7 @@ extern "C" {
     pub fn rst_ctx_device(ctx: *const rst_ctx, device: *mut c_int) -> c_int;
     pub fn rst_ctx_stream(ctx: *const rst_ctx, stream: *mut *mut c_void) -> c_int;
     pub fn rst_ctx_check_device(ctx: *mut rst_ctx) -> c_int;
+    pub fn rst_selftest_wait_expiry(ctx: *mut rst_ctx, limit_cycles: i64) -> c_int;
     pub fn rst_ctx_launch_count(ctx: *const rst_ctx, count: *mut u64) -> c_int;
     pub fn rst_ctx_memory_stats(ctx: *const rst_ctx, stats: *mut u64) -> c_int;
     pub fn rst_ctx_set_memory_limit(ctx: *mut rst_ctx, max_reserved_bytes: u64) -> c_int;
@@ -54,6 +55,7 @@ extern "C" {
     pub fn rst_tensor_download(t: *const rst_tensor, host: *mut c_double) -> c_int;
     pub fn rst_tensor_copy(dst: *mut rst_tensor, src: *const rst_tensor) -> c_int;
     pub fn rst_tensor_fill(t: *mut rst_tensor, value: c_double) -> c_int;
+    pub fn rst_tensor_checksum(t: *const rst_tensor, digest: *mut u64) -> c_int;
 
     // Linear
     pub fn rst_linear_forward(ctx: *mut rst_ctx, x: *const rst_tensor, w: *const rst_tensor,
@@ -120,6 +122,10 @@ extern "C" {
     pub fn rst_dataset_index_stage(d: *mut rst_dataset, batch: i64, host_indices: *mut *mut i64) -> c_int;
     pub fn rst_dataset_gather_staged(d: *mut rst_dataset, batch: i64, x: *mut rst_tensor,
                                      t: *mut rst_tensor) -> c_int;
+    pub fn rst_dataset_shuffle(d: *mut rst_dataset, seed: u64) -> c_int;
+    pub fn rst_dataset_gather_epoch(d: *mut rst_dataset, first: i64, batch: i64, x: *mut rst_tensor,
+                                    t: *mut rst_tensor) -> c_int;
+    pub fn rst_dataset_epoch_order(d: *mut rst_dataset, host_out: *mut i64) -> c_int;
 
     // data-parallel gradient exchange
     pub fn rst_comm_get_id(id_bytes: *mut c_void) -> c_int;

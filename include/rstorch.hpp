@@ -139,6 +139,14 @@ private:
     mutable uint64_t calls_ = 0;
 };
 
+// The initialiser of a Linear built without one: a single shared instance whose stream
+// index advances with every weight matrix it hands out, so that successive layers draw
+// independent weights as they do from the reference's thread generator (he.rs:13).
+inline const KaimingNormal& default_init() {
+    static const KaimingNormal shared;
+    return shared;
+}
+
 class Identity : public Module {   // activation/identity.rs:15-29
 public:
     Tensor forward(Tensor input) override { return input; }
@@ -199,18 +207,27 @@ private:
 
 class Linear : public Module {     // module/linear.rs
 public:
-    Linear(Context& ctx, size_t input_size, size_t output_size, const InitParameters& init = KaimingNormal())
+    Linear(Context& ctx, size_t input_size, size_t output_size, const InitParameters& init = default_init(),
+           bool with_bias = true)
         : in_(input_size), out_(output_size),
-          weight(ctx, (int64_t)output_size, (int64_t)input_size, init.weight(input_size, output_size)),
-          bias(ctx, 1, (int64_t)output_size, init.bias(input_size, output_size)) {}
+          weight(ctx, (int64_t)output_size, (int64_t)input_size, init.weight(input_size, output_size)) {
+        if (with_bias) bias = Tensor(ctx, 1, (int64_t)output_size, init.bias(input_size, output_size));
+    }
     static Linear new_with_kernel(Context& ctx, size_t input_size, size_t output_size, const InitParameters& init) {
         return Linear(ctx, input_size, output_size, init);
+    }
+    // A layer whose `bias` is None: the reference's struct holds `Option<Array2<f64>>` and
+    // branches on it (linear.rs:51-53, 65-67, 74-77) although its public constructors always
+    // fill it (:27).  y = x·Wᵀ, no db, one parameter pair.
+    static Linear without_bias(Context& ctx, size_t input_size, size_t output_size,
+                               const InitParameters& init = default_init()) {
+        return Linear(ctx, input_size, output_size, init, false);
     }
     Tensor forward(Tensor input) override { return forward_fused(std::move(input), false); }
     Tensor forward_fused(Tensor input, bool relu) {      // linear.rs:43-57 (+ relu.rs:21 in the epilogue)
         Tensor y = Tensor::like(input, input.nrows(), (int64_t)out_);
-        check(input.ctx(), rst_linear_forward(input.ctx(), input.handle(), weight.handle(), bias.handle(), relu ? 1 : 0,
-                                              y.handle()));
+        check(input.ctx(), rst_linear_forward(input.ctx(), input.handle(), weight.handle(),
+                                              bias ? bias.handle() : nullptr, relu ? 1 : 0, y.handle()));
         prev_input = input;
         return y;
     }
@@ -221,16 +238,17 @@ public:
         prev_input = Tensor();
         if (!grad_weight) {
             grad_weight = Tensor::like(x, (int64_t)out_, (int64_t)in_);
-            grad_bias = Tensor::like(x, 1, (int64_t)out_);
+            if (bias) grad_bias = Tensor::like(x, 1, (int64_t)out_);          // linear.rs:65
         }
         Tensor dx = need_input_grad ? Tensor::like(x, x.nrows(), x.ncols()) : Tensor();
         check(x.ctx(), rst_linear_backward(x.ctx(), gradient.handle(), x.handle(), weight.handle(),
                                            (relu_mask && dx) ? x.handle() : nullptr, grad_weight.handle(),
-                                           grad_bias.handle(), dx ? dx.handle() : nullptr));
+                                           bias ? grad_bias.handle() : nullptr, dx ? dx.handle() : nullptr));
         return dx;
     }
     Parameters parameters() override {                   // linear.rs:71-78
         if (!grad_weight) throw Panic(RST_ERR_STATE, "Linear::parameters before any backward (linear.rs:72 unwrap)");
+        if (!bias) return {{weight, grad_weight}};
         return {{weight, grad_weight}, {bias, grad_bias}};
     }
     size_t in_, out_;
@@ -312,7 +330,7 @@ private:
         for (size_t k = 0; k < n; ++k) {
             if (k % 2 == 0) {
                 Linear* lin = plain<Linear>(first + k);
-                if (!lin || lin->in_ * lin->out_ > kChainMaxWeightElems) return false;
+                if (!lin || !lin->bias || lin->in_ * lin->out_ > kChainMaxWeightElems) return false;
             } else if (!plain<ReLU>(first + k)) {
                 return false;
             }
@@ -409,6 +427,25 @@ public:
     }
 private:
     double lr_;
+};
+
+// BasicModel (model.rs:4-32): the reference's own statement of the training step and of
+// inference over a module, a loss and an optimiser.
+template <class M, class L, class O>
+class BasicModel {
+public:
+    BasicModel(M module, L loss, O optim) : module(std::move(module)), loss(std::move(loss)), optim(std::move(optim)) {}
+    void step(Tensor input, Tensor truth) {              // model.rs:19-27
+        Tensor pred = module.forward(std::move(input));
+        loss.forward(pred, std::move(truth));
+        Tensor gradient = loss.backward();
+        module.backward(std::move(gradient));
+        optim.step(module);
+    }
+    Tensor predict(Tensor input) { return module.forward(std::move(input)); }   // model.rs:29-31
+    M module;
+    L loss;
+    O optim;
 };
 
 inline double accuracy(const Tensor& pred, const Tensor& truth) {   // utils.rs:55-65

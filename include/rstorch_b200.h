@@ -79,6 +79,12 @@ int rst_ctx_stream(const rst_ctx* ctx, void** stream);
 /* Reads and clears the device-side status word written by kernels whose
  * bounded waits ran out; returns RST_ERR_DEVICE_TIMEOUT if it was set. */
 int rst_ctx_check_device(rst_ctx* ctx);
+/* Self-test of that path (no counterpart in the reference).  Launches one small GEMM whose
+ * producer copies nothing, so every consumer wait runs out after `limit_cycles` SM cycles
+ * (1..1e8); the kernel sets the status word, stores nothing and returns with no copy in
+ * flight.  The call itself succeeds; the next rst_ctx_check_device returns
+ * RST_ERR_DEVICE_TIMEOUT and clears the word, after which the context works as before. */
+int rst_selftest_wait_expiry(rst_ctx* ctx, int64_t limit_cycles);
 /* Number of kernels this library has launched through `ctx` so far. */
 int rst_ctx_launch_count(const rst_ctx* ctx, uint64_t* count);
 
@@ -106,6 +112,11 @@ int rst_tensor_upload(rst_tensor* t, const double* host);     /* blocking */
 int rst_tensor_download(const rst_tensor* t, double* host);   /* blocking */
 int rst_tensor_copy(rst_tensor* dst, const rst_tensor* src);  /* device to device */
 int rst_tensor_fill(rst_tensor* t, double value);
+/* 64-bit digest of the tensor's bit patterns in element order, computed on the device
+ * (no counterpart in the reference; blocking).  Equal digests mean bit-identical tensors up
+ * to a 2^-64 collision chance: the ranks of a data-parallel run compare the digests of
+ * their weights instead of moving the weights through the host. */
+int rst_tensor_checksum(const rst_tensor* t, uint64_t* digest);
 
 /* ---- Linear (src/module/linear.rs:41-79) ---------------------------------
  * forward:  Y[B,out] = X[B,in] · W[out,in]ᵀ + b[1,out]   (linear.rs:44-53);
@@ -278,6 +289,19 @@ int rst_dataset_gather(rst_dataset* d, const int64_t* indices, int64_t batch, rs
  * filled with NaN, and the next rst_ctx_check_device returns RST_ERR_INVALID_ARG. */
 int rst_dataset_index_stage(rst_dataset* d, int64_t batch, int64_t** host_indices);
 int rst_dataset_gather_staged(rst_dataset* d, int64_t batch, rst_tensor* X, rst_tensor* T);
+/* Shuffling on the device (`Shuffler::new` / `Shuffler::shuffle`,
+ * src/data/dataset/shuffler.rs:15-25, called by `DataLoader::iter_array` before every
+ * epoch, src/data/data_loader.rs:88-92).  The reference shuffles 0..len with an unseedable
+ * thread generator; rst_dataset_shuffle draws the epoch's order from `seed` with a kernel:
+ * position i maps to sample perm(i), a keyed bijection of [0, len) (four-round Feistel
+ * network over the smallest even bit width covering len, cycle-walked below len; round
+ * function splitmix64(seed + round·φ64 + right half)).  rst_dataset_gather_epoch builds the
+ * batch of epoch positions [first, first + batch) (`Shuffler::get`, shuffler.rs:31-33) with
+ * the same transform as rst_dataset_gather; positions beyond the dataset are rejected.
+ * rst_dataset_epoch_order downloads the current order (len entries; blocking). */
+int rst_dataset_shuffle(rst_dataset* d, uint64_t seed);
+int rst_dataset_gather_epoch(rst_dataset* d, int64_t first, int64_t batch, rst_tensor* X, rst_tensor* T);
+int rst_dataset_epoch_order(rst_dataset* d, int64_t* host_out);
 
 /* ---- data-parallel gradient exchange (no counterpart in the reference, which
  * is single-threaded; required to shard the batch over the GPUs of one box) --

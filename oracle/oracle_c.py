@@ -39,6 +39,8 @@ def load() -> C.CDLL:
         lib.orc_accuracy.restype = C.c_double
         lib.orc_softmax.restype = I64
         lib.orc_max_threads.restype = C.c_int
+        lib.orc_synth_uniform.restype = None
+        lib.orc_synth_normal.restype = None
         _lib = lib
     return _lib
 

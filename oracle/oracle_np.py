@@ -124,6 +124,38 @@ def iter_array_batch(images, labels, indices, classes):
     return X, T
 
 
+def epoch_permutation(seed: int, n: int) -> np.ndarray:
+    """Host mirror of the seeded epoch order that stands in for `Shuffler::shuffle`
+    (src/data/dataset/shuffler.rs:15-25, unseedable in the reference): position i maps to
+    sample perm(i), a four-round Feistel network over the smallest even bit width that covers
+    n, cycle-walked below n; round function splitmix64(seed + round·φ64 + right half)."""
+    M64 = (1 << 64) - 1
+    bits = 2
+    while bits < 62 and (1 << bits) < n:
+        bits += 2
+    half = bits // 2
+    mask = (1 << half) - 1
+
+    def mix(z: int) -> int:
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
+        return z ^ (z >> 31)
+
+    out = np.empty(n, dtype=np.int64)
+    for i in range(n):
+        v = i
+        while True:
+            l, r = v >> half, v & mask
+            for rnd in range(4):
+                f = mix((seed + 0x9E3779B97F4A7C15 * (rnd + 1) + r) & M64) & mask
+                l, r = r, l ^ f
+            v = (l << half) | r
+            if v < n:
+                break
+        out[i] = v
+    return out
+
+
 def mlp_step(weights, X, T, lr, skip_first_dx=False):
     """One step in the order of src/model.rs:19-27 for Linear,ReLU,...,Linear.
     Returns (loss, acc, grads, new_weights, logits)."""

@@ -50,8 +50,11 @@ int orc_max_threads(void) {
 #endif
 }
 
-// Implemented in oracle_gemm.cpp: C[M,N] (+)= A[M,K]·B[K,N], all row-major.
+// Implemented in oracle_gemm.cpp: C[M,N] = A[M,K]·B[K,N], all row-major.
 void orc_gemm_nn(int64_t M, int64_t N, int64_t K, const double* A, const double* B, double* C);
+// The same with strided operands: A(i,p) at A[i*sai + p*sak], B(p,j) at B[p*sbk + j*sbn].
+void orc_gemm_strided(int64_t M, int64_t N, int64_t K, const double* A, int64_t sai, int64_t sak, const double* B,
+                      int64_t sbk, int64_t sbn, double* C);
 // Same product with long-double accumulation, single thread (error bound for tests).
 void orc_gemm_precise(int64_t M, int64_t N, int64_t K, const double* A, const double* B, double* C);
 
@@ -69,10 +72,13 @@ static void transpose(const double* src, int64_t rows, int64_t cols, double* dst
 //   x += bias                        (:51-53)  broadcast of (1,out) over rows
 void orc_linear_forward(const double* X, const double* W, const double* b, int64_t B, int64_t in,
                         int64_t out, double* Y, int precise) {
-    std::vector<double> WT((size_t)in * out);
-    transpose(W, out, in, WT.data());
-    if (precise) orc_gemm_precise(B, out, in, X, WT.data(), Y);
-    else orc_gemm_nn(B, out, in, X, WT.data(), Y);
+    if (precise) {
+        std::vector<double> WT((size_t)in * out);
+        transpose(W, out, in, WT.data());
+        orc_gemm_precise(B, out, in, X, WT.data(), Y);
+    } else {
+        orc_gemm_strided(B, out, in, X, in, 1, W, 1, in, Y);          // weight.t() read in place
+    }
     if (b) {
 #pragma omp parallel for schedule(static)
         for (int64_t r = 0; r < B; ++r)
@@ -89,19 +95,27 @@ void orc_linear_backward(const double* dY, const double* X, const double* W, int
                          int64_t out, double* dW, double* db, double* dX, int precise) {
     const double n = (double)B;
     {
-        std::vector<double> dYT((size_t)B * out);
-        transpose(dY, B, out, dYT.data());
-        if (precise) orc_gemm_precise(out, in, B, dYT.data(), X, dW);
-        else orc_gemm_nn(out, in, B, dYT.data(), X, dW);
+        if (precise) {
+            std::vector<double> dYT((size_t)B * out);
+            transpose(dY, B, out, dYT.data());
+            orc_gemm_precise(out, in, B, dYT.data(), X, dW);
+        } else {
+            orc_gemm_strided(out, in, B, dY, 1, out, X, in, 1, dW);       // gradient.t() read in place
+        }
         const int64_t total = out * in;
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < total; ++i) dW[i] = dW[i] / n;
     }
     if (db) {
-        for (int64_t c = 0; c < out; ++c) db[c] = 0.0;
-        for (int64_t r = 0; r < B; ++r)
-            for (int64_t c = 0; c < out; ++c) db[c] += dY[r * out + c];
-        for (int64_t c = 0; c < out; ++c) db[c] = db[c] / n;
+        // every column summed over the rows in ascending order; threads take blocks of columns
+#pragma omp parallel for schedule(static)
+        for (int64_t c0 = 0; c0 < out; c0 += 512) {
+            const int64_t c1 = c0 + 512 < out ? c0 + 512 : out;
+            for (int64_t c = c0; c < c1; ++c) db[c] = 0.0;
+            for (int64_t r = 0; r < B; ++r)
+                for (int64_t c = c0; c < c1; ++c) db[c] += dY[r * out + c];
+            for (int64_t c = c0; c < c1; ++c) db[c] = db[c] / n;
+        }
     }
     if (dX) {
         if (precise) orc_gemm_precise(B, in, out, dY, W, dX);
@@ -208,6 +222,39 @@ double orc_accuracy(const double* pred, const double* truth, int64_t rows, int64
     int64_t hit = 0;
     for (int64_t r = 0; r < rows; ++r) hit += (a[r] == b[r]);
     return (double)hit / (double)rows;
+}
+
+// Seeded input streams: an independent restatement of the generator that produces the
+// benchmark's synthetic weights and batches, so that the CPU arm of the benchmark needs
+// nothing from the library it is compared with.  Word i of stream `key` is
+// splitmix64(key + (i+1)·0x9E3779B97F4A7C15); a uniform takes the top 53 bits; a normal is
+// Box-Muller over words 2i and 2i+1.  tests/test_oracle.py checks both against the
+// library's generator bit for bit.
+static inline uint64_t synth_word(uint64_t key, uint64_t index) {
+    uint64_t z = key + index * 0x9E3779B97F4A7C15ull + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+static inline double synth_unit(uint64_t w) { return (double)(w >> 11) * (1.0 / 9007199254740992.0); }
+
+void orc_synth_uniform(uint64_t key, uint64_t n, uint64_t offset, double* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) out[i] = synth_unit(synth_word(key, offset + (uint64_t)i));
+}
+
+void orc_synth_normal(uint64_t key, uint64_t n, uint64_t offset, double mean, double stddev, double* out) {
+    const double two_pi = 6.283185307179586476925286766559;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        const uint64_t e = offset + (uint64_t)i;
+        const double u1 = 1.0 - synth_unit(synth_word(key, 2 * e));       // (0, 1]
+        const double u2 = synth_unit(synth_word(key, 2 * e + 1));
+        const double radius = std::sqrt(-2.0 * std::log(u1));
+        const double v = radius * std::cos(two_pi * u2);
+        const double scaled = stddev * v;
+        out[i] = mean + scaled;
+    }
 }
 
 // Whole training steps of an MLP `Linear, ReLU, Linear, ReLU, ..., Linear` in the

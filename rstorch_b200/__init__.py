@@ -16,6 +16,7 @@ from ._lib import RstError, exported_symbols
 from .core import Context, Graph, Tensor, Timer
 from .data import ArrayDataset, DataLoader, DeviceDataset, SequentialSampler
 from .loss import CrossEntropyLoss, Loss
+from .model import BasicModel
 from .module import (Identity, InitParameters, KaimingNormal, Linear, Module, Normal, Parameter, ReLU,
                      Sequential, Softmax, XavierNormal, sequential)
 from .optim import SGD, Optimizer
@@ -27,6 +28,6 @@ __all__ = [
     "DeviceDataset",
     "SequentialSampler", "CrossEntropyLoss", "Loss", "Identity", "InitParameters", "KaimingNormal",
     "Linear", "Module", "Normal", "Parameter", "ReLU", "Sequential", "Softmax", "XavierNormal", "sequential",
-    "SGD", "Optimizer",
+    "SGD", "Optimizer", "BasicModel",
     "Communicator", "backward_with_exchange", "shard_rows", "accuracy", "argmax", "one_hot",
 ]

@@ -49,6 +49,7 @@ _SIGNATURES = {
     "rst_ctx_device": [P, C.POINTER(C.c_int)],
     "rst_ctx_stream": [P, PP],
     "rst_ctx_check_device": [P],
+    "rst_selftest_wait_expiry": [P, I64],
     "rst_ctx_launch_count": [P, C.POINTER(U64)],
     "rst_ctx_memory_stats": [P, C.POINTER(U64)],
     "rst_ctx_set_memory_limit": [P, U64],
@@ -62,6 +63,7 @@ _SIGNATURES = {
     "rst_tensor_download": [P, P],
     "rst_tensor_copy": [P, P],
     "rst_tensor_fill": [P, DBL],
+    "rst_tensor_checksum": [P, C.POINTER(U64)],
     "rst_linear_forward": [P, P, P, P, C.c_int, P],
     "rst_linear_backward": [P, P, P, P, P, P, P, P],
     "rst_linear_backward_chain": [P, C.c_int, P, P, P, P, P, P, P],
@@ -93,6 +95,9 @@ _SIGNATURES = {
     "rst_dataset_gather": [P, C.POINTER(I64), I64, P, P],
     "rst_dataset_index_stage": [P, I64, C.POINTER(C.POINTER(I64))],
     "rst_dataset_gather_staged": [P, I64, P, P],
+    "rst_dataset_shuffle": [P, U64],
+    "rst_dataset_gather_epoch": [P, I64, I64, P, P],
+    "rst_dataset_epoch_order": [P, C.POINTER(I64)],
     "rst_comm_get_id": [P],
     "rst_comm_create": [P, P, C.c_int, C.c_int, PP],
     "rst_comm_destroy": [P],

@@ -18,7 +18,6 @@ class Context:
         check(self._lib.rst_ctx_create(int(device), C.byref(h)))
         self.handle = h
         self.device = int(device)
-        self._keepalive = None      # list while a graph capture is recording, else None
         self._next_slot = 0
 
     # -- lifecycle ---------------------------------------------------------
@@ -40,11 +39,6 @@ class Context:
     def empty(self, rows: int, cols: int) -> "Tensor":
         h = C.c_void_p()
         self._check(self._lib.rst_tensor_alloc(self.handle, int(rows), int(cols), C.byref(h)))
-        if self._keepalive is not None:
-            # Allocated while a graph is being captured: the graph has this address
-            # baked in, so the graph owns the block and frees it when it is destroyed.
-            self._keepalive.append(Tensor(self, h, int(rows), int(cols)))
-            return Tensor(self, C.c_void_p(h.value), int(rows), int(cols), owns=False)
         return Tensor(self, h, int(rows), int(cols))
 
     def zeros(self, rows: int, cols: int) -> "Tensor":
@@ -168,6 +162,12 @@ class Tensor:
         self.t = None
         return self
 
+    def checksum(self) -> int:
+        """64-bit digest of the bit patterns, computed on the device (blocking)."""
+        v = C.c_uint64()
+        self.ctx._check(self.ctx._lib.rst_tensor_checksum(self.handle, C.byref(v)))
+        return int(v.value)
+
     def clone(self) -> "Tensor":
         t = self.ctx.empty(self.rows, self.cols)
         self.ctx._check(self.ctx._lib.rst_tensor_copy(t.handle, self.handle))
@@ -190,12 +190,7 @@ class Tensor:
             self.handle = C.c_void_p()
             ctx = self.ctx
             if not self._owns or ctx.handle is None or not ctx.handle.value:
-                return                      # a graph or the (destroyed) context owns the memory
-            if ctx._keepalive is not None:
-                # freed while a graph is being captured: captured kernels may read or
-                # write it, so it stays out of the allocator until the graph goes
-                ctx._keepalive.append(Tensor(ctx, h, self.rows, self.cols, self._base))
-                return
+                return                      # something else, or the (destroyed) context, owns the memory
             ctx._lib.rst_tensor_free(h)
 
     def __del__(self):
@@ -244,8 +239,12 @@ class Timer:
 
 
 class Graph:
-    def __init__(self, ctx: Context, handle, keepalive: list):
-        self.ctx, self.handle, self._keepalive = ctx, handle, keepalive
+    """A recorded step.  The library keeps every block the recorded kernels address out of
+    its allocator until the graph is destroyed, so tensors made during the capture may be
+    dropped freely; tensors made before it (weights, inputs) must outlive the graph."""
+
+    def __init__(self, ctx: Context, handle):
+        self.ctx, self.handle = ctx, handle
 
     def launch(self) -> None:
         self.ctx._check(self.ctx._lib.rst_graph_launch(self.handle))
@@ -254,9 +253,6 @@ class Graph:
         if self.handle is not None and self.handle.value and self.ctx.handle.value:
             self.ctx._lib.rst_graph_destroy(self.handle)
             self.handle = C.c_void_p()
-            keep, self._keepalive = self._keepalive, []
-            for t in keep:
-                t.free()
 
     def __del__(self):
         try:
@@ -266,8 +262,9 @@ class Graph:
 
 
 class GraphCapture:
-    """Records one step into a CUDA graph.  Run the same step eagerly once before,
-    so that every allocation of the captured run is served from the cache."""
+    """Records one step into a CUDA graph.  Nothing is allocated from the driver while
+    recording: run the same step once, unrecorded, directly before each capture, so that
+    every allocation of the recorded run is served from the allocator's cache."""
 
     def __init__(self, ctx: Context):
         self.ctx = ctx
@@ -275,17 +272,14 @@ class GraphCapture:
 
     def __enter__(self) -> "GraphCapture":
         self.ctx._check(self.ctx._lib.rst_graph_capture_begin(self.ctx.handle))
-        self.ctx._keepalive = []
         return self
 
     def __exit__(self, exc_type, exc, tb) -> bool:
-        keep, self.ctx._keepalive = self.ctx._keepalive, None
         h = C.c_void_p()
         status = self.ctx._lib.rst_graph_capture_end(self.ctx.handle, C.byref(h))
         if exc_type is None:
             self.ctx._check(status)
-            self.graph = Graph(self.ctx, h, keep)
-        else:
-            for t in keep:
-                t.free()
+            self.graph = Graph(self.ctx, h)
+        elif status == 0 and h.value:
+            self.ctx._lib.rst_graph_destroy(h)
         return False

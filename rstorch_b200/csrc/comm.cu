@@ -7,6 +7,7 @@
 // NCCL is resolved at run time (dlopen) so the library loads on hosts without
 // it and shares whichever libnccl the process already has.
 #include <dlfcn.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <cstring>
 
@@ -135,6 +136,7 @@ extern "C" int rst_allreduce_avg(rst_comm* m, int n, rst_tensor* const* tensors)
     for (int i = 0; i < n; ++i) RST_TRY(check_tensor(c, tensors[i], "tensors[i]"));
     if (n == 0) return RST_OK;
     NcclApi& api = nccl();
+    struct Range { Range() { nvtxRangePushA("allreduce_avg"); } ~Range() { nvtxRangePop(); } } range;
     // the exchange starts once the gradients queued so far on the compute stream exist
     RST_CUDA(c, cudaEventRecord(m->ready, c->compute));
     RST_CUDA(c, cudaStreamWaitEvent(c->comm, m->ready, 0));

@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
 #include <utility>
 #include <vector>
@@ -43,11 +44,23 @@ public:
     void empty_cache();
     void set_limit(uint64_t max_reserved) { limit_ = max_reserved; }
 
+    // Graph capture.  Between begin_recording and end_recording every block that is
+    // handed out or handed back is remembered: the recorded kernels have its address
+    // baked in.  end_recording takes the remembered blocks that sit in the cache out of
+    // it (*cached: the graph owns them until it is destroyed) and lists the ones a
+    // tensor still holds (*live: they go to the graph when that tensor is freed).
+    void begin_recording();
+    void end_recording(std::vector<std::pair<void*, size_t>>* cached, std::vector<void*>* live);
+    // A block that a graph took out of the cache counts as in use until the graph returns it.
+    void adopt(size_t granted) { in_use += granted; peak = peak > in_use ? peak : in_use; }
+
     uint64_t in_use = 0, reserved = 0, peak = 0, requests = 0, hits = 0, driver_allocs = 0;
 
 private:
     std::multimap<size_t, void*> free_;
     uint64_t limit_ = 0;
+    bool recording_ = false;
+    std::map<void*, size_t> recorded_;
 };
 
 struct ResultSlot {  // written by the xent kernel, copied to pinned host memory
@@ -104,6 +117,12 @@ struct rst_ctx {
     std::vector<ProfRecord> prof_records;
     std::vector<cudaEvent_t> prof_event_pool;
     std::map<std::string, rst_sgd_plan*> plan_cache;
+
+    // Blocks that a live graph has recorded while a tensor still holds them: freeing the
+    // tensor hands the block to that graph instead of the cache.
+    std::map<void*, rst_graph*> graph_pinned;
+    // Kernels whose dynamic shared-memory limit has been raised on this context's device.
+    std::set<const void*> smem_attr_done;
 };
 
 namespace rst {
@@ -189,6 +208,8 @@ struct GemmArgs {
     double* colsum_out;       // optional [M]: Σ_k A(m,k) / divisor when A is M-major (db)
     double* C_transposed;     // optional [N,M]: a second, transposed copy of C (M-major A with N-major B
                               // and large tiles only; the caller checks gemm_writes_transposed)
+    long long wait_limit_cycles;  // 0 = the default bound of a barrier wait (about two seconds)
+    bool starve_producer;     // self-test only: no tile is ever copied, every consumer wait runs out
 };
 // Whether launch_gemm would honour C_transposed for this product.
 bool gemm_writes_transposed(const rst_ctx* ctx, const GemmArgs& a);
@@ -205,6 +226,8 @@ int launch_relu_forward(rst_ctx* ctx, const double* x, double* y, int64_t n);
 int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, double* dx,
                          int64_t n);
 int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n);
+// Adds the digest of x[0..n) to *d_out (a zeroed device word).
+int launch_checksum(rst_ctx* ctx, const double* x, int64_t n, unsigned long long* d_out);
 int launch_transpose(rst_ctx* ctx, const double* src, int64_t rows, int64_t cols, double* dst);
 int launch_softmax_axis0(rst_ctx* ctx, const double* x, double* p, int64_t rows, int64_t cols);
 int launch_softmax_jacobian_diag(rst_ctx* ctx, double* J, int64_t n);

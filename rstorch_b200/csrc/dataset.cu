@@ -68,6 +68,52 @@ gather_normalize_onehot_kernel(const unsigned char* __restrict__ images, const u
     }
 }
 
+// Epoch permutation drawn on the device (Shuffler::new / Shuffler::shuffle,
+// src/data/dataset/shuffler.rs:15-25, which shuffle 0..len with an unseedable thread
+// generator).  Here position i of the epoch maps to sample perm(i), where perm is a keyed
+// bijection of [0, n): a four-round Feistel network over the smallest even number of bits
+// that covers n, walked until the value falls below n (cycle walking keeps it a bijection).
+// Every position is computed independently, so no sort and no host round trip is needed,
+// and a host mirror of these few lines reproduces it bit for bit.
+__host__ __device__ __forceinline__ unsigned long long perm_mix(unsigned long long z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__host__ __device__ __forceinline__ long long epoch_permute(unsigned long long seed, int half_bits,
+                                                            unsigned long long n, unsigned long long i) {
+    const unsigned long long mask = (1ull << half_bits) - 1ull;
+    unsigned long long v = i;
+    do {
+        unsigned long long l = v >> half_bits, r = v & mask;
+#pragma unroll
+        for (int round = 0; round < 4; ++round) {
+            const unsigned long long f = perm_mix(seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(round + 1) + r) & mask;
+            const unsigned long long nl = r;
+            r = l ^ f;
+            l = nl;
+        }
+        v = (l << half_bits) | r;
+    } while (v >= n);
+    return (long long)v;
+}
+
+__global__ void __launch_bounds__(kGatherThreads)
+epoch_permutation_kernel(unsigned long long seed, int half_bits, long long n, long long* __restrict__ perm) {
+    grid_dependency_release();
+    grid_dependency_wait();
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        perm[i] = epoch_permute(seed, half_bits, (unsigned long long)n, (unsigned long long)i);
+}
+
+int feistel_half_bits(long long n) {
+    int bits = 2;
+    while (bits < 62 && (1ll << bits) < n) bits += 2;
+    return bits / 2;
+}
+
 }  // namespace
 
 struct rst_dataset {
@@ -86,6 +132,9 @@ struct rst_dataset {
     long long* h_stage;
     long long* d_stage;
     long long stage_cap;
+    // the current epoch's order of the samples (rst_dataset_shuffle); identity until then
+    long long* d_perm;
+    bool shuffled;
 };
 
 extern "C" int rst_dataset_destroy(rst_dataset* d);
@@ -107,6 +156,7 @@ extern "C" int rst_dataset_create_u8(rst_ctx* c, const unsigned char* images, co
     d->ctx = c; d->n = n; d->features = (int)features; d->classes = (int)classes;
     d->d_images = nullptr; d->d_labels = nullptr; d->idx_cap = 0; d->next_slot = 0;
     d->h_stage = nullptr; d->d_stage = nullptr; d->stage_cap = 0;
+    d->d_perm = nullptr; d->shuffled = false;
     for (int s = 0; s < kIndexSlots; ++s) { d->h_idx[s] = nullptr; d->d_idx[s] = nullptr; d->idx_free[s] = nullptr; d->slot_used[s] = false; }
     bool okay = cudaMalloc((void**)&d->d_images, (size_t)n * features) == cudaSuccess &&
                 cudaMalloc((void**)&d->d_labels, (size_t)n) == cudaSuccess &&
@@ -136,6 +186,7 @@ extern "C" int rst_dataset_destroy(rst_dataset* d) {
     }
     if (d->h_stage) cudaFreeHost(d->h_stage);
     if (d->d_stage) cudaFree(d->d_stage);
+    if (d->d_perm) cudaFree(d->d_perm);
     cudaGetLastError();
     delete d;
     return RST_OK;
@@ -249,4 +300,57 @@ extern "C" int rst_dataset_gather_staged(rst_dataset* d, int64_t batch, rst_tens
     RST_CUDA(c, cudaMemcpyAsync(d->d_stage, d->h_stage, (size_t)batch * sizeof(long long), cudaMemcpyHostToDevice,
                                 c->compute));
     return launch_gather(d, d->d_stage, batch, X, T);
+}
+
+// ---- seeded epoch order on the device ------------------------------------------------
+// rst_dataset_shuffle draws the order of the next epoch (Shuffler::shuffle, called by
+// DataLoader::iter_array before every epoch, src/data/data_loader.rs:88-92);
+// rst_dataset_gather_epoch builds the batch of epoch positions [first, first + batch),
+// i.e. of samples perm[first .. first + batch), what ArrayDataLoaderIter::next does through
+// Shuffler::get (shuffler.rs:31-33).  No sample index crosses the host bus.
+extern "C" int rst_dataset_shuffle(rst_dataset* d, uint64_t seed) {
+    if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
+    rst_ctx* c = d->ctx;
+    if (!d->d_perm) {
+        if (c->capturing) return fail(c, RST_ERR_STATE, "the first shuffle allocates; call it before capturing");
+        if (cudaMalloc((void**)&d->d_perm, (size_t)d->n * sizeof(long long)) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(c, RST_ERR_OOM, "cannot allocate the epoch order of %lld samples", d->n);
+        }
+    }
+    long long blocks = (d->n + kGatherThreads - 1) / kGatherThreads;
+    const long long cap = (long long)c->num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    launch_step_kernel(c, c->compute, epoch_permutation_kernel, dim3((unsigned)blocks), dim3(kGatherThreads), 0,
+                       (unsigned long long)seed, feistel_half_bits(d->n), d->n, d->d_perm);
+    RST_TRY(after_launch(c, "epoch_permutation_kernel"));
+    d->shuffled = true;
+    return RST_OK;
+}
+
+extern "C" int rst_dataset_epoch_order(rst_dataset* d, int64_t* host_out) {
+    if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
+    rst_ctx* c = d->ctx;
+    if (!host_out) return fail(c, RST_ERR_INVALID_ARG, "host_out is NULL");
+    if (c->capturing) return fail(c, RST_ERR_STATE, "blocking call during graph capture");
+    if (!d->shuffled) {
+        for (long long i = 0; i < d->n; ++i) host_out[i] = i;       // never shuffled: sampler order
+        return RST_OK;
+    }
+    RST_CUDA(c, cudaMemcpyAsync(host_out, d->d_perm, (size_t)d->n * sizeof(long long), cudaMemcpyDeviceToHost,
+                                c->compute));
+    RST_CUDA(c, cudaStreamSynchronize(c->compute));
+    return RST_OK;
+}
+
+extern "C" int rst_dataset_gather_epoch(rst_dataset* d, int64_t first, int64_t batch, rst_tensor* X, rst_tensor* T) {
+    if (!d || !valid(d->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad dataset");
+    rst_ctx* c = d->ctx;
+    RST_TRY(check_batch_tensors(d, batch, X, T));
+    if (!d->shuffled) return fail(c, RST_ERR_STATE, "rst_dataset_gather_epoch before rst_dataset_shuffle");
+    // `dataset.get(index)?` ends the reference's epoch on a missing sample (data_loader.rs:197)
+    if (first < 0 || first + batch > d->n)
+        return fail(c, RST_ERR_INVALID_ARG, "epoch positions [%lld, %lld) outside the dataset of %lld samples",
+                    (long long)first, (long long)(first + batch), d->n);
+    return launch_gather(d, d->d_perm + first, batch, X, T);
 }

@@ -157,6 +157,24 @@ __global__ void __launch_bounds__(kThreads) colsum_pass2(const double* __restric
     out[col] = acc / n;
 }
 
+// Order-sensitive 64-bit digest of a tensor's bit patterns: Σ_i mix(bits_i + (i+1)·φ64)
+// in wrapping arithmetic.  Integer addition commutes, so the result does not depend on the
+// grid or on the order in which blocks finish.
+__global__ void __launch_bounds__(kThreads) checksum_kernel(const double* __restrict__ x, int64_t n,
+                                                            unsigned long long* __restrict__ out) {
+    unsigned long long acc = 0ull;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        unsigned long long z = (unsigned long long)__double_as_longlong(x[i]) + (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        acc += z ^ (z >> 31);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0 && acc) atomicAdd(out, acc);
+}
+
 inline int grid_for(const rst_ctx* ctx, int64_t work_items, int per_sm) {
     int64_t blocks = (work_items + kThreads - 1) / kThreads;
     int64_t cap = (int64_t)ctx->num_sms * per_sm;
@@ -201,6 +219,12 @@ int launch_transpose(rst_ctx* ctx, const double* src, int64_t rows, int64_t cols
     if (tiles > 0x7fffffffLL) return fail(ctx, RST_ERR_UNSUPPORTED, "matrix too large to transpose in one launch");
     transpose_kernel<<<(unsigned)tiles, kThreads, 0, ctx->compute>>>(src, dst, rows, cols);
     return after_launch(ctx, "transpose_kernel");
+}
+
+int launch_checksum(rst_ctx* ctx, const double* x, int64_t n, unsigned long long* d_out) {
+    if (n == 0) return RST_OK;
+    checksum_kernel<<<grid_for(ctx, n, 8), kThreads, 0, ctx->compute>>>(x, n, d_out);
+    return after_launch(ctx, "checksum_kernel");
 }
 
 int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n) {
@@ -258,8 +282,9 @@ static __device__ __align__(256) double g_noalloc_colsum_scratch[kNoAllocScratch
 // shadow symbol); the device address is looked up once per device.
 std::mutex g_noalloc_mutex;
 double* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {nullptr};
+int g_noalloc_sm_count[kNoAllocMaxDevices] = {0};
 
-int noalloc_scratch_for_current_device(double** out) {
+int noalloc_scratch_for_current_device(double** out, int* sm_count) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess)
@@ -275,9 +300,16 @@ int noalloc_scratch_for_current_device(double** out) {
             return fail(nullptr, RST_ERR_CUDA, "cudaGetSymbolAddress of the static scratch failed on device %d: %s",
                         dev, cudaGetErrorString(e));
         }
+        int sms = 0;      // an attribute query; it allocates nothing
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+            cudaGetLastError();
+            sms = kNumSMsFallback;
+        }
+        g_noalloc_sm_count[dev] = sms;
         g_noalloc_scratch_ptr[dev] = p;
     }
     *out = g_noalloc_scratch_ptr[dev];
+    *sm_count = g_noalloc_sm_count[dev];
     return RST_OK;
 }
 
@@ -296,12 +328,13 @@ extern "C" int rst_bias_grad_noalloc(const double* dY, int64_t rows, int64_t col
                     "use rst_linear_backward, which may allocate",
                     (long long)cols, (long long)kNoAllocScratchDoubles);
     double* scratch = nullptr;
-    RST_TRY(noalloc_scratch_for_current_device(&scratch));
+    int sm_count = 0;
+    RST_TRY(noalloc_scratch_for_current_device(&scratch, &sm_count));
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
     // as many row parts as fit the fixed scratch, up to about four waves of blocks
     const int64_t col_blocks = (cols + kColsPerBlock - 1) / kColsPerBlock;
-    int64_t parts = (148 * 4 + col_blocks - 1) / col_blocks;
+    int64_t parts = ((int64_t)sm_count * 4 + col_blocks - 1) / col_blocks;
     const int64_t fit = kNoAllocScratchDoubles / cols;          // >= 1 by the check above
     if (parts > fit) parts = fit;
     const int64_t by_rows = (rows + 63) / 64;

@@ -37,12 +37,14 @@ struct GemmParams {
     double* Ct;             // [N][M]: optional transposed copy of C (splits == 1, M-major A, N-major B)
     int* status;
     double divisor;
+    long long wait_limit;   // SM cycles a barrier wait may take before the kernel gives up
     long long M, N, K;
     int tiles_m, tiles_n;
     int k_tiles;            // ceil(K / 16)
     int k_tiles_per_split;
     int splits;
     int epilogue;
+    int starve;             // self-test: the producer issues no copy, so every consumer wait runs out
 };
 
 __device__ __forceinline__ double apply_epilogue(const GemmParams& p, double v, long long r, long long c) {
@@ -168,14 +170,14 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
 
     if (warp == C_::kConsumerWarps) {
         // ---------------- producer warp: one lane drives TMA ----------------
-        if (lane == 0) {
+        if (lane == 0 && !p.starve) {
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmB);
             int it = 0;
             for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u)) {
+                if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, p.wait_limit)) {
                     atomicExch(p.status, kDevBarrierTimeout);
                     atomicExch(p.status + 1, 1);
                     break;
@@ -287,7 +289,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
             for (int nt = 0; nt < NT; ++nt) dmma_m16n8k8(acc[mt][nt], a[mt], b[nt]);
     };
     auto wait_full = [&](int it) -> bool {
-        if (mbar_wait_bounded(full_bar(it % STAGES), (uint32_t)(it / STAGES) & 1u)) return true;
+        if (mbar_wait_bounded(full_bar(it % STAGES), (uint32_t)(it / STAGES) & 1u, p.wait_limit)) return true;
         atomicExch(p.status, kDevBarrierTimeout);
         atomicExch(p.status + 1, 2);
         return false;       // results are invalid from here on
@@ -511,6 +513,15 @@ gemm_f64_plain(const double* __restrict__ A, const double* __restrict__ B, long 
     }
 }
 
+// Raises a kernel's dynamic shared-memory limit once per context (the attribute belongs to
+// the device the context is bound to).
+int allow_dynamic_smem(rst_ctx* ctx, const void* kernel, int bytes) {
+    if (ctx->smem_attr_done.count(kernel)) return RST_OK;
+    RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    ctx->smem_attr_done.insert(kernel);
+    return RST_OK;
+}
+
 int encode_map(rst_ctx* ctx, CUtensorMap* map, const double* base, long long inner, long long outer,
                int box_inner, int box_outer) {
     auto fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ctx->encode_tiled);
@@ -532,11 +543,7 @@ template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B
 int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
     auto kernel = gemm_f64_tma_dmma<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM, WRITE_T>;
-    static bool attr_set[16] = {false};   // per device
-    if (!attr_set[ctx->device & 15]) {
-        RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes));
-        attr_set[ctx->device & 15] = true;
-    }
+    RST_TRY(allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kernel), C_::kSmemBytes));
     CUtensorMap tmA, tmB;
     if (A_K) RST_TRY(encode_map(ctx, &tmA, a.A, a.K, a.M, kBK, BM));
     else     RST_TRY(encode_map(ctx, &tmA, a.A, a.M, a.K, 16, kBK));
@@ -652,6 +659,8 @@ int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done) {
     p.C = a.C; p.bias = a.bias; p.mask_src = a.mask_src; p.splitk_ws = nullptr;
     p.colsum_out = nullptr;
     p.status = ctx->d_status; p.divisor = a.divisor;
+    p.wait_limit = a.wait_limit_cycles > 0 ? a.wait_limit_cycles : kWaitLimitCycles;
+    p.starve = a.starve_producer ? 1 : 0;
     p.M = a.M; p.N = a.N; p.K = a.K; p.epilogue = a.epilogue; p.splits = 1;
     if (a.C_transposed) {
         if (!gemm_writes_transposed(ctx, a))
@@ -734,6 +743,7 @@ int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped) 
         GemmParams& p = gp.p[slot];
         p.C = a.C; p.bias = a.bias; p.mask_src = a.mask_src; p.colsum_out = a.colsum_out;
         p.status = ctx->d_status; p.divisor = a.divisor;
+        p.wait_limit = kWaitLimitCycles;
         p.M = a.M; p.N = a.N; p.K = a.K; p.epilogue = a.epilogue;
         p.tiles_m = (int)((a.M + kSmallBM - 1) / kSmallBM);
         p.tiles_n = (int)((a.N + kSmallBN - 1) / kSmallBN);
@@ -761,11 +771,7 @@ int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped) 
     }
 
     auto kernel = gemm_f64_tma_dmma_grouped<kSmallBM, kSmallBN, kSmallWM, kSmallWN, kSmallStages, false, false, true>;
-    static bool attr_set[16] = {false};   // per device
-    if (!attr_set[ctx->device & 15]) {
-        RST_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C_::kSmemBytes));
-        attr_set[ctx->device & 15] = true;
-    }
+    RST_TRY(allow_dynamic_smem(ctx, reinterpret_cast<const void*>(kernel), C_::kSmemBytes));
     launch_step_kernel(ctx, ctx->compute, kernel, dim3((unsigned)cta), dim3(C_::kThreads), (size_t)C_::kSmemBytes,
                        maps, gp);
     RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma_grouped"));

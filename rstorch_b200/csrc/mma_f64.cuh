@@ -62,17 +62,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Waits for the phase with the given parity to complete, for at most about two
-// seconds of SM clock.  Returns false when the limit is reached.
+// Waits for the phase with the given parity to complete, for at most `limit_cycles` of
+// SM clock (the default is about two seconds).  Returns false when the limit is reached.
 constexpr long long kWaitLimitCycles = 4000000000LL;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > kWaitLimitCycles) return false;
+        if (clock64() - t0 > limit_cycles) return false;
     }
 }
 

@@ -238,6 +238,34 @@ extern "C" int rst_linear_backward_chain(rst_ctx* c, int n, const rst_tensor* dY
     return RST_OK;
 }
 
+// Self-test of the bounded device-side waits.  One small product (64x64x64) is launched
+// with its producer disabled, so no tile is ever copied: every consumer warp's wait on the
+// first stage runs out after `limit_cycles`, the kernel writes the device status word,
+// stores nothing and returns with no copy in flight.  The next rst_ctx_check_device then
+// reports RST_ERR_DEVICE_TIMEOUT and clears the word; the context stays usable.
+extern "C" int rst_selftest_wait_expiry(rst_ctx* c, int64_t limit_cycles) {
+    RST_TRY(need_ctx(c));
+    if (limit_cycles < 1 || limit_cycles > 100000000LL)
+        return fail(c, RST_ERR_INVALID_ARG, "limit_cycles must be in [1, 1e8] (at most a twentieth of a second)");
+    if (c->capturing) return fail(c, RST_ERR_STATE, "self-test during graph capture");
+    rst_tensor *A = nullptr, *B = nullptr, *C = nullptr;
+    int s = rst_tensor_alloc(c, 64, 64, &A);
+    if (s == RST_OK) s = rst_tensor_alloc(c, 64, 64, &B);
+    if (s == RST_OK) s = rst_tensor_alloc(c, 64, 64, &C);
+    if (s == RST_OK) {
+        GemmArgs g{};
+        g.A = A->data; g.B = B->data; g.C = C->data;
+        g.M = 64; g.N = 64; g.K = 64;
+        g.a_kmajor = true; g.b_kmajor = true;
+        g.epilogue = kEpiNone; g.divisor = 1.0;
+        g.wait_limit_cycles = limit_cycles;
+        g.starve_producer = true;
+        s = launch_gemm(c, g);
+    }
+    rst_tensor_free(A); rst_tensor_free(B); rst_tensor_free(C);   // stream-ordered reuse
+    return s;
+}
+
 extern "C" int rst_relu_forward(rst_ctx* c, const rst_tensor* X, rst_tensor* Y) {
     RST_TRY(need_ctx(c));
     RST_TRY(check_tensor(c, X, "X"));

@@ -1,5 +1,6 @@
 // Host runtime: context, caching allocator, device tensors, timers, graph capture.
 #include <cudaTypedefs.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <cstring>
@@ -77,7 +78,11 @@ static cudaEvent_t prof_event(rst_ctx* ctx) {
     return e;
 }
 
+// Every launch group also opens an NVTX range named after its kernel class (gemm_fwd,
+// gemm_dW, gemm_dX, colsum, xent, sgd, ...), so a timeline tool shows the step's phases.
+// Without a tool attached the NVTX calls are no-ops of a few nanoseconds.
 ProfScope::ProfScope(rst_ctx* ctx, const char* name) : ctx_(ctx), index_(-1) {
+    nvtxRangePushA(name);
     if (!ctx->profiling || ctx->capturing) return;
     rst_ctx::ProfRecord r{name, prof_event(ctx), prof_event(ctx)};
     if (!r.start || !r.stop) return;
@@ -88,6 +93,7 @@ ProfScope::ProfScope(rst_ctx* ctx, const char* name) : ctx_(ctx), index_(-1) {
 
 ProfScope::~ProfScope() {
     if (index_ >= 0) cudaEventRecord(ctx_->prof_records[(size_t)index_].stop, ctx_->compute);
+    nvtxRangePop();
 }
 
 // ------------------------------ allocator -----------------------------------
@@ -118,6 +124,7 @@ void* CachingAllocator::allocate(size_t bytes, size_t* granted, int* err, bool m
         hits++;
         in_use += *granted;
         peak = std::max(peak, in_use);
+        if (recording_) recorded_[p] = *granted;
         return p;
     }
     if (!may_call_driver) { *err = -2; return nullptr; }
@@ -145,6 +152,34 @@ void CachingAllocator::release(void* ptr, size_t granted) {
     if (!ptr) return;
     in_use -= granted;
     free_.emplace(granted, ptr);
+    // recorded kernels may read or write a block that is handed back while recording
+    if (recording_) recorded_[ptr] = granted;
+}
+
+void CachingAllocator::begin_recording() {
+    recording_ = true;
+    recorded_.clear();
+}
+
+void CachingAllocator::end_recording(std::vector<std::pair<void*, size_t>>* cached, std::vector<void*>* live) {
+    recording_ = false;
+    for (const auto& rec : recorded_) {
+        bool in_cache = false;
+        auto range = free_.equal_range(rec.second);
+        for (auto it = range.first; it != range.second; ++it)
+            if (it->second == rec.first) {
+                free_.erase(it);
+                in_cache = true;
+                break;
+            }
+        if (in_cache) {
+            if (cached) cached->emplace_back(rec.first, rec.second);
+            else free_.emplace(rec.second, rec.first);        // capture failed: nothing pins it
+        } else if (live) {
+            live->push_back(rec.first);
+        }
+    }
+    recorded_.clear();
 }
 
 void CachingAllocator::empty_cache() {
@@ -247,8 +282,9 @@ extern "C" int rst_ctx_create(int device, rst_ctx** out) {
         CTX_CUDA(cudaStreamCreateWithPriority(&c->comm, cudaStreamNonBlocking, greatest));
         CTX_CUDA(cudaStreamCreateWithPriority(&c->copy, cudaStreamNonBlocking, greatest));
     }
-    CTX_CUDA(cudaMalloc((void**)&c->d_status, 4 * sizeof(int)));
-    CTX_CUDA(cudaMemset(c->d_status, 0, 4 * sizeof(int)));
+    // words 0-3: device status; words 4-5: the 64-bit accumulator of rst_tensor_checksum
+    CTX_CUDA(cudaMalloc((void**)&c->d_status, 8 * sizeof(int)));
+    CTX_CUDA(cudaMemset(c->d_status, 0, 8 * sizeof(int)));
     CTX_CUDA(cudaMallocHost((void**)&c->h_status, 4 * sizeof(int)));
     CTX_CUDA(cudaMalloc((void**)&c->d_results, kXentSlots * sizeof(ResultSlot)));
     CTX_CUDA(cudaMemset(c->d_results, 0, kXentSlots * sizeof(ResultSlot)));
@@ -371,6 +407,8 @@ extern "C" int rst_ctx_empty_cache(rst_ctx* c) {
 }
 
 // ------------------------------ tensors ----------------------------------------
+static void graph_adopt_block(rst_graph* g, void* ptr, size_t granted);
+
 extern "C" int rst_tensor_alloc(rst_ctx* c, int64_t rows, int64_t cols, rst_tensor** out) {
     if (!valid(c)) return fail(nullptr, RST_ERR_INVALID_ARG, "not a live context");
     if (!out) return fail(c, RST_ERR_INVALID_ARG, "out is NULL");
@@ -384,13 +422,14 @@ extern "C" int rst_tensor_alloc(rst_ctx* c, int64_t rows, int64_t cols, rst_tens
     size_t granted = 0;
     int err = 0;
     RST_CUDA(c, cudaSetDevice(c->device));
-    void* p = c->alloc.allocate(bytes, &granted, &err, true);
+    void* p = c->alloc.allocate(bytes, &granted, &err, !c->capturing);
     if (!p) {
         if (err == -1)
             return fail(c, RST_ERR_OOM, "allocation of %zu bytes exceeds the memory limit", bytes);
         if (err == -2)
-            return fail(c, RST_ERR_STATE, "allocation of %zu bytes misses the cache during graph "
-                        "capture; run the step once before capturing", bytes);
+            return fail(c, RST_ERR_STATE, "allocation of %zu bytes misses the cache during graph capture "
+                        "(no driver allocation is made while recording); run the same step once, "
+                        "unrecorded, directly before every capture", bytes);
         return fail(c, RST_ERR_OOM, "cudaMalloc of %zu bytes failed: %s", bytes,
                     cudaGetErrorString((cudaError_t)err));
     }
@@ -416,7 +455,18 @@ extern "C" int rst_tensor_slice(rst_tensor* parent, int64_t off, int64_t rows, i
 extern "C" int rst_tensor_free(rst_tensor* t) {
     if (!t) return RST_OK;
     if (!valid(t)) return fail(nullptr, RST_ERR_FOREIGN_HANDLE, "not a live tensor handle");
-    if (t->owns) t->ctx->alloc.release(t->data, t->granted);
+    if (t->owns) {
+        rst_ctx* c = t->ctx;
+        auto pin = c->graph_pinned.find(t->data);
+        if (pin != c->graph_pinned.end()) {
+            // a live graph writes or reads this block on every replay: it goes to the
+            // graph, which returns it to the cache when it is destroyed
+            graph_adopt_block(pin->second, t->data, t->granted);
+            c->graph_pinned.erase(pin);
+        } else {
+            c->alloc.release(t->data, t->granted);
+        }
+    }
     t->magic = kDeadMagic;
     delete t;
     return RST_OK;
@@ -471,6 +521,24 @@ extern "C" int rst_tensor_copy(rst_tensor* dst, const rst_tensor* src) {
     if (bytes)
         RST_CUDA(c, cudaMemcpyAsync(dst->data, src->data, bytes, cudaMemcpyDeviceToDevice,
                                     c->compute));
+    return RST_OK;
+}
+
+// 64-bit digest of the tensor's bit patterns, computed on the device: two tensors have the
+// same digest exactly when (up to a 2^-64 collision chance) they hold the same bits in the
+// same order.  Data-parallel replicas compare digests instead of moving weights to the host.
+extern "C" int rst_tensor_checksum(const rst_tensor* t, uint64_t* out) {
+    if (!valid(t)) return fail(nullptr, RST_ERR_FOREIGN_HANDLE, "not a live tensor handle");
+    rst_ctx* c = t->ctx;
+    if (!out) return fail(c, RST_ERR_INVALID_ARG, "out is NULL");
+    if (c->capturing) return fail(c, RST_ERR_STATE, "blocking call during graph capture");
+    unsigned long long* d_word = reinterpret_cast<unsigned long long*>(c->d_status + 4);
+    RST_CUDA(c, cudaMemsetAsync(d_word, 0, sizeof(unsigned long long), c->compute));
+    RST_TRY(launch_checksum(c, t->data, t->rows * t->cols, d_word));
+    unsigned long long host = 0;
+    RST_CUDA(c, cudaMemcpyAsync(&host, d_word, sizeof host, cudaMemcpyDeviceToHost, c->compute));
+    RST_CUDA(c, cudaStreamSynchronize(c->compute));
+    *out = host;
     return RST_OK;
 }
 
@@ -567,7 +635,15 @@ struct rst_graph {
     cudaGraph_t graph;
     cudaGraphExec_t exec;
     uint64_t launches_per_replay;
+    // Blocks the recorded kernels address and no tensor holds any more.  They stay out of
+    // the cache while the graph lives, so that no later allocation is handed memory that a
+    // replay overwrites.
+    std::vector<std::pair<void*, size_t>> blocks;
 };
+
+static void graph_adopt_block(rst_graph* g, void* ptr, size_t granted) {
+    g->blocks.emplace_back(ptr, granted);      // stays counted as in use until the graph goes
+}
 
 static thread_local uint64_t g_capture_launch_base = 0;
 
@@ -576,6 +652,7 @@ extern "C" int rst_graph_capture_begin(rst_ctx* c) {
     if (c->capturing) return fail(c, RST_ERR_STATE, "capture already in progress");
     RST_CUDA(c, cudaStreamBeginCapture(c->compute, cudaStreamCaptureModeRelaxed));
     c->capturing = true;
+    c->alloc.begin_recording();
     g_capture_launch_base = c->launches;
     return RST_OK;
 }
@@ -588,6 +665,7 @@ extern "C" int rst_graph_capture_end(rst_ctx* c, rst_graph** out) {
     cudaError_t e = cudaStreamEndCapture(c->compute, &g);
     if (e != cudaSuccess || !g) {
         cudaGetLastError();
+        c->alloc.end_recording(nullptr, nullptr);
         return fail(c, RST_ERR_CUDA, "cudaStreamEndCapture failed: %s", cudaGetErrorString(e));
     }
     cudaGraphExec_t ex = nullptr;
@@ -595,11 +673,17 @@ extern "C" int rst_graph_capture_end(rst_ctx* c, rst_graph** out) {
     if (e != cudaSuccess) {
         cudaGraphDestroy(g);
         cudaGetLastError();
+        c->alloc.end_recording(nullptr, nullptr);
         return fail(c, RST_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
     }
     uint64_t per = c->launches - g_capture_launch_base;
     c->launches = g_capture_launch_base;   // captured launches have not run yet
-    *out = new rst_graph{c, g, ex, per};
+    rst_graph* graph = new rst_graph{c, g, ex, per, {}};
+    std::vector<void*> live;
+    c->alloc.end_recording(&graph->blocks, &live);
+    for (const auto& b : graph->blocks) c->alloc.adopt(b.second);
+    for (void* p : live) c->graph_pinned[p] = graph;     // a later graph that records it takes over
+    *out = graph;
     return RST_OK;
 }
 
@@ -618,6 +702,12 @@ extern "C" int rst_graph_destroy(rst_graph* g) {
     if (valid(g->ctx) && !g->ctx->capturing) cudaStreamSynchronize(g->ctx->compute);
     cudaGraphExecDestroy(g->exec);
     cudaGraphDestroy(g->graph);
+    if (valid(g->ctx)) {
+        rst_ctx* c = g->ctx;
+        for (const auto& b : g->blocks) c->alloc.release(b.first, b.second);
+        for (auto it = c->graph_pinned.begin(); it != c->graph_pinned.end();)
+            it = (it->second == g) ? c->graph_pinned.erase(it) : std::next(it);
+    }
     delete g;
     return RST_OK;
 }

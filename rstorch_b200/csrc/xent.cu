@@ -490,7 +490,7 @@ int dispatch_rows(rst_ctx* ctx, const double* logits, const double* truth, doubl
                        logits, truth, out, rows, c, partials, counter, d_slot)
 #define XENT_BLOCK_CASE(EPT)                                                                          \
     launch_step_kernel(ctx, st, xent_block_kernel<EPT, MODE>,                                         \
-                       dim3((unsigned)std::min<int64_t>(rows, max_grid)), dim3(kXentThreads), 0,      \
+                       dim3((unsigned)std::max<int64_t>(1, std::min<int64_t>(rows, max_grid))), dim3(kXentThreads), 0, \
                        logits, truth, out, rows, c, partials, counter, d_slot)
     if (cols <= 16) XENT_CASE(4, 4);
     else if (cols <= 32) XENT_CASE(8, 4);

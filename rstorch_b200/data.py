@@ -68,6 +68,22 @@ class DeviceDataset:
         into a graph; each replay uses the indices the stage holds at that moment."""
         self.ctx._check(self.ctx._lib.rst_dataset_gather_staged(self.handle, int(batch), X.handle, T.handle))
 
+    def shuffle(self, seed: int) -> None:
+        """Draws the order of the next epoch on the device (`Shuffler::shuffle`,
+        src/data/dataset/shuffler.rs:22-25): a keyed bijection of [0, len)."""
+        self.ctx._check(self.ctx._lib.rst_dataset_shuffle(self.handle, int(seed) & 0xFFFFFFFFFFFFFFFF))
+
+    def epoch_order(self) -> np.ndarray:
+        """The current epoch's order of the samples (identity before the first shuffle)."""
+        out = np.empty(self.n, dtype=np.int64)
+        self.ctx._check(self.ctx._lib.rst_dataset_epoch_order(self.handle, out.ctypes.data_as(C.POINTER(C.c_int64))))
+        return out
+
+    def gather_epoch(self, first: int, batch: int, X: Tensor, T: Tensor) -> None:
+        """Builds the batch of epoch positions [first, first + batch) (`Shuffler::get`,
+        shuffler.rs:31-33); no sample index leaves the device."""
+        self.ctx._check(self.ctx._lib.rst_dataset_gather_epoch(self.handle, int(first), int(batch), X.handle, T.handle))
+
     def close(self) -> None:
         if self.handle is not None and self.handle.value and self.ctx.handle.value:
             self.ctx._lib.rst_dataset_destroy(self.handle)
@@ -97,12 +113,20 @@ class DataLoader:
     indices and, like the reference, ends the epoch at the first batch it cannot
     fill (the remainder is dropped, data_loader.rs:69-71,197).  The reference's
     shuffle draws from an unseedable thread RNG (dataset/shuffler.rs:15-25); here
-    it is a permutation from `shuffle_seed`, redrawn at every `iter_array` call."""
+    it is a permutation from `shuffle_seed`, redrawn at every `iter_array` call
+    (data_loader.rs:88-92).  Over a `DeviceDataset` the permutation is drawn by a
+    kernel and stays on the device: epoch e uses the key `synth.stream_key(
+    shuffle_seed, "shuffle", e)`."""
 
     def __init__(self, dataset: ArrayDataset, batch_size: int, shuffle: bool, sampler: SequentialSampler,
-                 ctx: Context, slots: int = 2, shuffle_seed: int = 0):
+                 ctx: Context, slots: int = 2, shuffle_seed: int = 0, prefetch: bool = False):
+        """`prefetch=True` assembles batches on a helper thread: while the GPU runs step k
+        the thread gathers the rows of batch k+2 into a pinned slot and the copy stream
+        moves batch k+1 to the device (use three slots to keep all three in flight)."""
         self.dataset, self.batch_size, self.sampler, self.ctx = dataset, int(batch_size), sampler, ctx
+        self._prefetch = bool(prefetch)
         self._shuffle = bool(shuffle)
+        self._shuffle_seed, self._epoch = int(shuffle_seed), 0
         self._rng = np.random.default_rng(shuffle_seed)
         self._slots = int(slots)
         self._stager = None
@@ -132,11 +156,45 @@ class DataLoader:
         t = np.ctypeslib.as_array(pt, shape=(b, self.dataset.targets.shape[1]))
         return x, t
 
+    def _assemble(self, views, indices: np.ndarray) -> None:
+        """`ArrayDataLoaderIter::next` (data_loader.rs:192-207): the rows of the batch's
+        samples, one after the other, into the two batch arrays.  The indices were checked
+        against the dataset when the epoch's order was made, so `clip` never alters one; it
+        only spares numpy's bounds-checking mode its temporary copy of the output."""
+        x, t = views
+        np.take(self.dataset.samples, indices, axis=0, out=x, mode="clip")
+        np.take(self.dataset.targets, indices, axis=0, out=t, mode="clip")
+
     def _fill(self, slot: int, indices: np.ndarray) -> None:
-        x, t = self._host_views(slot)
-        np.take(self.dataset.samples, indices, axis=0, out=x)
-        np.take(self.dataset.targets, indices, axis=0, out=t)
+        self._assemble(self._host_views(slot), indices)
         self.ctx._check(self.ctx._lib.rst_stager_submit(self._stager, slot))
+
+    def _iter_prefetched(self, order: np.ndarray) -> Iterator[tuple[Tensor, Tensor]]:
+        """Host assembly of batch k+2 (helper thread), the host-to-device copy of batch k+1
+        (copy stream) and the caller's work on batch k overlap.  Only the main thread calls
+        the library; the helper thread touches the pinned host arrays alone."""
+        import concurrent.futures as cf
+        b, S, lib = self.batch_size, self._slots, self.ctx._lib
+        n_batches = len(order) // b
+        if n_batches == 0:
+            return
+        with cf.ThreadPoolExecutor(max_workers=1) as pool:
+            def start(k):
+                # rst_stager_host waits until the previous copy out of this pinned slot is done
+                return pool.submit(self._assemble, self._host_views(k % S), order[k * b:(k + 1) * b])
+
+            pending = {k: start(k) for k in range(min(2, n_batches, S))}
+            pending.pop(0).result()
+            self.ctx._check(lib.rst_stager_submit(self._stager, 0))
+            for k in range(n_batches):
+                if k + 1 < n_batches:
+                    if k + 1 not in pending:             # fewer than three slots: assembled only now
+                        pending[k + 1] = start(k + 1)
+                    pending.pop(k + 1).result()
+                    self.ctx._check(lib.rst_stager_submit(self._stager, (k + 1) % S))
+                if k + 2 < n_batches and S >= 3:
+                    pending[k + 2] = start(k + 2)
+                yield self._acquire(k % S)
 
     def _acquire(self, slot: int) -> tuple[Tensor, Tensor]:
         lib, ctx = self.ctx._lib, self.ctx
@@ -159,16 +217,41 @@ class DataLoader:
             ds.gather(order[k * b:(k + 1) * b], X, T)
             yield X, T
 
+    def _iter_device_shuffled(self) -> Iterator[tuple[Tensor, Tensor]]:
+        """Epoch of a shuffled DeviceDataset under the sequential sampler: the order is drawn
+        and consumed on the device."""
+        from . import synth
+        ds, b = self.dataset, self.batch_size
+        ds.shuffle(synth.stream_key(self._shuffle_seed, "shuffle", self._epoch))
+        self._epoch += 1
+        ring = max(2, self._slots)
+        if getattr(self, "_out_ring", None) is None or len(self._out_ring) != ring:
+            self._out_ring = [(self.ctx.empty(b, ds.features), self.ctx.empty(b, ds.classes)) for _ in range(ring)]
+        for k in range(min(self.sampler.size, len(ds)) // b):
+            X, T = self._out_ring[k % ring]
+            ds.gather_epoch(k * b, b, X, T)
+            yield X, T
+
     def iter_array(self) -> Iterator[tuple[Tensor, Tensor]]:
+        if self._shuffle and isinstance(self.dataset, DeviceDataset) and isinstance(self.sampler, SequentialSampler):
+            yield from self._iter_device_shuffled()
+            return
         order = np.fromiter(self.sampler.iter(), dtype=np.int64)
+        # `dataset.get(index)?` returns None at the first index the dataset does not hold and
+        # that ends the epoch (data_loader.rs:197): later indices are never looked at
+        missing = np.flatnonzero((order < 0) | (order >= len(self.dataset)))
+        if missing.size:
+            order = order[:missing[0]]
         if self._shuffle:
             perm = self._rng.permutation(len(self.dataset))
             order = perm[order]
         if isinstance(self.dataset, DeviceDataset):
-            yield from self._iter_device(order[order < len(self.dataset)])
+            yield from self._iter_device(order)
             return
         self._ensure_stager()
-        order = order[order < len(self.dataset)] if (order >= len(self.dataset)).any() else order
+        if self._prefetch and self._slots >= 2:
+            yield from self._iter_prefetched(order)
+            return
         n_batches = len(order) // self.batch_size
         b = self.batch_size
         # keep `slots - 1` batches in flight ahead of the one being consumed

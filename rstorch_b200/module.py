@@ -55,6 +55,19 @@ class KaimingNormal(InitParameters):
             output_size, input_size)
 
 
+# The initialiser a `Linear` gets when none is passed.  The reference draws every layer
+# from the thread generator (he.rs:13), so successive layers are independent; one shared
+# instance, whose stream index advances with every weight matrix it hands out, gives the
+# same property (layer k built in a process draws stream ("weight", k) of seed 0).
+_default_init = KaimingNormal(0)
+
+
+def reset_default_init(seed: int = 0) -> None:
+    """Restarts the default initialiser's stream counter (tests and reproducible scripts)."""
+    global _default_init
+    _default_init = KaimingNormal(seed)
+
+
 class XavierNormal(InitParameters):
     """N(0, sqrt(2 / (input_size + output_size))) weights (module/init/xavier.rs:9-15)."""
 
@@ -190,11 +203,13 @@ class Linear(Module):
     """y = x·Wᵀ + b (module/linear.rs).  `weight` is (out, in), `bias` (1, out)."""
 
     def __init__(self, input_size: int, output_size: int, init: InitParameters | None = None,
-                 ctx: Context | None = None):
-        init = init if init is not None else KaimingNormal()
+                 ctx: Context | None = None, bias: bool = True):
+        init = init if init is not None else _default_init
         self.input_size, self.output_size = int(input_size), int(output_size)
         self._host_weight = np.ascontiguousarray(init.weight(input_size, output_size), dtype=np.float64)
-        self._host_bias = np.ascontiguousarray(init.bias(input_size, output_size), dtype=np.float64)
+        self.has_bias = bool(bias)
+        self._host_bias = (np.ascontiguousarray(init.bias(input_size, output_size), dtype=np.float64)
+                           if self.has_bias else None)
         self.weight: Tensor | None = None
         self.bias: Tensor | None = None
         self.prev_input: Tensor | None = None
@@ -208,11 +223,21 @@ class Linear(Module):
                         ctx: Context | None = None) -> "Linear":
         return cls(input_size, output_size, init, ctx)
 
+    @classmethod
+    def without_bias(cls, input_size: int, output_size: int, init: InitParameters | None = None,
+                     ctx: Context | None = None) -> "Linear":
+        """A layer whose `bias` is `None`.  The reference's struct holds `bias:
+        Option<Array2<f64>>` and branches on it in forward, backward and parameters
+        (linear.rs:51-53, 65-67, 74-77), although its public constructors always fill
+        it (:27); this constructor reaches those branches: y = x·Wᵀ, no db, one
+        parameter pair."""
+        return cls(input_size, output_size, init, ctx, bias=False)
+
     def to(self, ctx: Context) -> "Linear":
         """Uploads the parameters (done lazily by the first forward otherwise)."""
         if self.weight is None or self.weight.ctx is not ctx:
             self.weight = ctx.tensor(self._host_weight)
-            self.bias = ctx.tensor(self._host_bias)
+            self.bias = ctx.tensor(self._host_bias) if self.has_bias else None
         return self
 
     # -- forward -------------------------------------------------------------
@@ -224,7 +249,8 @@ class Linear(Module):
         self.to(ctx)
         out = ctx.empty(input.rows, self.output_size)
         ctx._check(ctx._lib.rst_linear_forward(ctx.handle, input.handle, self.weight.handle,
-                                               self.bias.handle, 1 if fuse_relu else 0, out.handle))
+                                               self.bias.handle if self.has_bias else None,
+                                               1 if fuse_relu else 0, out.handle))
         self.prev_input = input               # moved in, not copied (linear.rs:55)
         return out
 
@@ -248,7 +274,8 @@ class Linear(Module):
         # gradients are overwritten, never accumulated (linear.rs:63,66)
         if self.grad_weight is None or self.grad_weight.ctx is not ctx:
             self.grad_weight = ctx.empty(self.output_size, self.input_size)
-            self.grad_bias = ctx.empty(1, self.output_size)
+            self.grad_bias = ctx.empty(1, self.output_size) if self.has_bias else None   # linear.rs:65
+        db = self.grad_bias.handle if self.has_bias else None
         dx = ctx.empty(x.rows, x.cols) if need_input_grad else None
         mask = x.handle if (relu_mask and dx is not None) else None
         large = (dx is not None and x.rows * x.cols >= self._TRANSPOSED_GRADIENT_MIN_ELEMS
@@ -256,7 +283,7 @@ class Linear(Module):
         if not large:
             ctx._check(ctx._lib.rst_linear_backward(
                 ctx.handle, gradient.handle, x.handle, self.weight.handle, mask,
-                self.grad_weight.handle, self.grad_bias.handle, dx.handle if dx is not None else None))
+                self.grad_weight.handle, db, dx.handle if dx is not None else None))
             return dx
         if gradient.t is None:              # the loss gradient: make the first companion
             gradient.t = ctx.empty(gradient.cols, gradient.rows)
@@ -265,14 +292,16 @@ class Linear(Module):
             dx.t = ctx.empty(x.cols, x.rows)
         ctx._check(ctx._lib.rst_linear_backward_t(
             ctx.handle, gradient.handle, gradient.t.handle, x.handle, self.weight.handle, mask,
-            self.grad_weight.handle, self.grad_bias.handle, dx.handle,
+            self.grad_weight.handle, db, dx.handle,
             dx.t.handle if dx.t is not None else None))
         return dx
 
     def parameters(self) -> list[Parameter]:
-        if self.grad_weight is None or self.grad_bias is None:
+        if self.grad_weight is None or (self.has_bias and self.grad_bias is None):
             raise RuntimeError("Linear::parameters called before any backward "
                                "(the reference panics on `grad_weight.as_mut().unwrap()`, linear.rs:72)")
+        if not self.has_bias:                                   # linear.rs:74-77
+            return [Parameter(self.weight, self.grad_weight)]
         return [Parameter(self.weight, self.grad_weight), Parameter(self.bias, self.grad_bias)]
 
 
@@ -376,7 +405,8 @@ class Sequential(Module):
         chain: list[tuple[Linear, ReLU | None]] = []
         for k, layer in enumerate(layers):
             if k % 2 == 0:
-                if not self._plain(layer, Linear) or layer.input_size * layer.output_size > self._CHAIN_MAX_WEIGHT_ELEMS:
+                if (not self._plain(layer, Linear) or not layer.has_bias
+                        or layer.input_size * layer.output_size > self._CHAIN_MAX_WEIGHT_ELEMS):
                     return None
                 chain.append((layer, layers[k - 1] if k else None))
             elif not self._plain(layer, ReLU):

@@ -87,6 +87,28 @@ static void unit_tests(Context& ctx) {
         EXPECT(module.remove(99) == nullptr);
         EXPECT(module.remove(4) != nullptr && module.len() == 4);
     }
+    {   // default initialiser: every layer draws its own stream (he.rs:13 draws from the thread generator)
+        Linear a(ctx, 100, 100), b(ctx, 100, 100);
+        EXPECT(a.weight.to_host() != b.weight.to_host());
+    }
+    {   // bias: None (linear.rs:51-53, 65-67, 74-77): y = x·Wᵀ, no db, one parameter pair
+        Linear m = Linear::without_bias(ctx, 2, 1, FixedInit());
+        Tensor y = m.forward(Tensor(ctx, 3, 2, {1.0, 2.0, 3.0, -4.0, -5.0, -6.0}));
+        EXPECT(close_to(y.to_host(), {2.0, 1.0, -8.0}));
+        Tensor dx = m.backward(Tensor(ctx, 3, 1, {1.0, 1.0, 1.0}));
+        EXPECT(close_to(dx.to_host(), {1.0, 0.5, 1.0, 0.5, 1.0, 0.5}));
+        EXPECT(m.parameters().size() == 1 && !m.grad_bias);
+        EXPECT(close_to(m.grad_weight.to_host(), {-1.0 / 3.0, -8.0 / 3.0}));
+    }
+    {   // BasicModel::step / predict (model.rs:19-31)
+        BasicModel<Sequential, CrossEntropyLoss, SGD> model(
+            sequential(Linear(ctx, 3, 8), ReLU(), Linear(ctx, 8, 2)), CrossEntropyLoss(), SGD(0.1));
+        Tensor x(ctx, 2, 3, {1.0, 2.0, 3.0, -4.0, -5.0, -6.0}), t(ctx, 2, 2, {1.0, 0.0, 0.0, 1.0});
+        std::vector<double> before = model.predict(x).to_host();
+        model.step(x, t);
+        std::vector<double> after = model.predict(x).to_host();
+        EXPECT(before.size() == 4 && after.size() == 4 && before != after);
+    }
     {   // the reference's unwrap() panics
         bool threw = false;
         try { Linear(ctx, 2, 2).backward(Tensor(ctx, 1, 2, {0.0, 0.0})); } catch (const Panic&) { threw = true; }

@@ -161,3 +161,82 @@ def test_staged_gather_eager_and_replayed(ctx):
         ds.gather_staged(48, ctx.empty(48, 35), T)
     assert e.value.status == _lib.RST_ERR_SHAPE
     ds.close()
+
+
+def test_epoch_order_is_drawn_on_the_device_and_matches_the_host_mirror(ctx):
+    """`Shuffler::shuffle` on the device (shuffler.rs:22-25): the kernel's permutation is
+    compared bit for bit with its host mirror, and batches gathered through it with the
+    README transform of the mirrored indices."""
+    images, labels = synth.mnist_like_u8(5, 0, 1000, side=5, classes=6)
+    ds = rt.DeviceDataset(ctx, images, labels, 6)
+    assert np.array_equal(ds.epoch_order(), np.arange(1000))          # never shuffled: sampler order
+    X, T = ctx.empty(64, 25), ctx.empty(64, 6)
+    with pytest.raises(rt.RstError) as e:
+        ds.gather_epoch(0, 64, X, T)
+    assert e.value.status == _lib.RST_ERR_STATE
+    for seed in (0, 1, 0xFFFFFFFFFFFFFFFF):
+        ds.shuffle(seed)
+        want = on.epoch_permutation(seed, 1000)
+        assert np.array_equal(ds.epoch_order(), want)
+        for first in (0, 64, 936):
+            ds.gather_epoch(first, 64, X, T)
+            want_x, want_t = on.iter_array_batch(images, labels, want[first:first + 64], 6)
+            assert np.array_equal(X.numpy(), want_x, equal_nan=True) and np.array_equal(T.numpy(), want_t)
+    with pytest.raises(rt.RstError) as e:
+        ds.gather_epoch(960, 64, X, T)                                # runs past the dataset: the epoch ends
+    assert e.value.status == _lib.RST_ERR_INVALID_ARG
+    # sizes around the powers of four that change the Feistel width
+    for n in (1, 2, 5, 16, 17, 255, 257):
+        small = rt.DeviceDataset(ctx, images[:n], labels[:n], 6)
+        small.shuffle(9)
+        assert np.array_equal(small.epoch_order(), on.epoch_permutation(9, n))
+        small.close()
+    ctx.check_device()
+    ds.close()
+
+
+def test_shuffled_loader_over_a_device_dataset_keeps_the_order_on_the_device(ctx):
+    images, labels = synth.mnist_like_u8(6, 0, 200, side=4, classes=5)
+    ds = rt.DeviceDataset(ctx, images, labels, 5)
+    dl = rt.DataLoader(ds, 32, True, rt.SequentialSampler(len(ds)), ctx, shuffle_seed=4)
+    for epoch in range(2):
+        got = [(x.numpy(), t.numpy()) for x, t in dl.iter_array()]
+        assert len(got) == 6                                          # 8 left-over samples are dropped
+        order = on.epoch_permutation(synth.stream_key(4, "shuffle", epoch), 200)
+        for k, (x, t) in enumerate(got):
+            want_x, want_t = on.iter_array_batch(images, labels, order[k * 32:(k + 1) * 32], 5)
+            assert np.array_equal(x, want_x, equal_nan=True) and np.array_equal(t, want_t)
+    ds.close()
+
+
+def test_epoch_ends_at_the_first_missing_sample(ctx):
+    """`dataset.get(index)?` (data_loader.rs:197): a sampler index outside the dataset ends
+    the epoch there; indices after it are never used."""
+    class Skipping:
+        size = 12
+
+        def iter(self):
+            return iter([0, 1, 2, 3, 4, 5, 99, 6, 7, 8, 9, 10])
+
+    X = np.arange(40, dtype=np.float64).reshape(10, 4)
+    T = np.eye(10)
+    dl = rt.DataLoader(rt.ArrayDataset(X, T), 2, False, Skipping(), ctx)
+    got = [x.numpy() for x, _ in dl.iter_array()]
+    assert len(got) == 3 and np.array_equal(np.concatenate(got), X[:6])
+    dl.close()
+
+
+def test_prefetching_loader_yields_the_same_batches(ctx):
+    rng = np.random.default_rng(0)
+    X, T = rng.standard_normal((230, 12)), rng.standard_normal((230, 3))
+    ds = rt.ArrayDataset(X, T)
+    for slots in (2, 3, 4):
+        plain = rt.DataLoader(ds, 16, True, rt.SequentialSampler(len(ds)), ctx, slots=slots, shuffle_seed=1)
+        ahead = rt.DataLoader(ds, 16, True, rt.SequentialSampler(len(ds)), ctx, slots=slots, shuffle_seed=1,
+                              prefetch=True)
+        a = [(x.numpy(), t.numpy()) for x, t in plain.iter_array()]
+        b = [(x.numpy(), t.numpy()) for x, t in ahead.iter_array()]
+        assert len(a) == len(b) == 14
+        for (xa, ta), (xb, tb) in zip(a, b):
+            assert np.array_equal(xa, xb) and np.array_equal(ta, tb)
+        plain.close(); ahead.close()

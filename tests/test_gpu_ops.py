@@ -124,6 +124,74 @@ def test_linear_forward_backward_parity(ctx, oc, B, cin, cout):
     ctx.check_device()
 
 
+@pytest.mark.parametrize("B,cin,cout", [(3, 5, 7), (32, 100, 10), (257, 130, 66), (2048, 1024, 2048)])
+def test_linear_without_bias_parity(ctx, oc, B, cin, cout):
+    """`bias: None` (linear.rs:51-53, 65-67, 74-77): b = NULL forward, db = NULL backward,
+    the ReLU that cannot ride in a bias-less epilogue, and the one-pair parameter list."""
+    rng = np.random.default_rng(B + cin + cout)
+    X, W = rng.standard_normal((B, cin)), rng.standard_normal((cout, cin)) / np.sqrt(cin)
+    X[X < -0.5] = 0.0
+    dY = rng.standard_normal((B, cout))
+    lin = rt.Linear.without_bias(cin, cout, Fixed(W, np.zeros((1, cout))))
+    xd = ctx.tensor(X)
+    y = lin.forward(xd).numpy()
+    assert rel_err(y, oc.linear_forward(X, W, None)) < REL_TOL
+    dx = lin.backward(ctx.tensor(dY)).numpy()
+    dW, _, dX = oc.linear_backward(dY, X, W, want_db=False)
+    assert rel_err(lin.grad_weight.numpy(), dW) < REL_TOL and rel_err(dx, dX) < REL_TOL
+    assert lin.grad_bias is None and lin.bias is None
+    params = lin.parameters()
+    assert len(params) == 1 and params[0].parm is lin.weight
+    # fused call sites: ReLU after a bias-less product, mask in dX
+    y_relu = lin._forward(xd, fuse_relu=True).numpy()
+    assert np.array_equal(y_relu, np.maximum(y, 0.0))
+    dx_masked = lin._backward(ctx.tensor(dY), relu_mask=True, need_input_grad=True).numpy()
+    assert np.array_equal(dx_masked, dx * (X > 0.0))
+    # inside a container, next to layers that do have a bias; SGD moves the one tensor it is given
+    seq = rt.sequential(rt.Linear.new_with_kernel(cin, cout, Fixed(W, np.ones((1, cout)))), rt.ReLU(),
+                        rt.Linear.without_bias(cout, 4, Fixed(np.ones((4, cout)), np.zeros((1, 4)))))
+    out = seq.forward(xd)
+    seq.backward(ctx.tensor(np.ones((B, 4))))
+    assert out.shape == (B, 4) and len(seq.parameters()) == 3
+    before = seq.layers[2].weight.numpy()
+    rt.SGD.new(0.5).step(seq)
+    assert np.array_equal(seq.layers[2].weight.numpy(), oc.sgd_step(before, seq.layers[2].grad_weight.numpy(), 0.5))
+    ctx.check_device()
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable(ctx, oc):
+    """A kernel whose producer never copies a tile: every consumer wait runs out after the
+    given limit, the kernel reports it through the status word and returns; the next check
+    returns RST_ERR_DEVICE_TIMEOUT, clears the word, and ordinary launches pass parity."""
+    ctx.check_device()
+    ctx._check(ctx._lib.rst_selftest_wait_expiry(ctx.handle, 100_000))
+    with pytest.raises(rt.RstError) as e:
+        ctx.check_device()
+    assert e.value.status == _lib.RST_ERR_DEVICE_TIMEOUT and "bounded wait" in str(e.value)
+    ctx.check_device()                                     # cleared
+    rng = np.random.default_rng(5)
+    X, W, b = rng.standard_normal((64, 64)), rng.standard_normal((64, 64)), rng.standard_normal((1, 64))
+    lin = rt.Linear.new_with_kernel(64, 64, Fixed(W, b))
+    assert rel_err(lin.forward(ctx.tensor(X)).numpy(), oc.linear_forward(X, W, b)) < REL_TOL
+    ctx.check_device()
+    assert ctx._lib.rst_selftest_wait_expiry(ctx.handle, 0) == _lib.RST_ERR_INVALID_ARG
+    assert ctx._lib.rst_selftest_wait_expiry(ctx.handle, 10**9) == _lib.RST_ERR_INVALID_ARG
+
+
+def test_tensor_checksum_tells_bit_patterns_apart(ctx):
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((300, 77))
+    t1, t2 = ctx.tensor(a), ctx.tensor(a)
+    assert t1.checksum() == t2.checksum() == t1.checksum()
+    b = a.copy(); b[17, 3] = np.nextafter(b[17, 3], np.inf)         # one ulp
+    assert ctx.tensor(b).checksum() != t1.checksum()
+    c = a.copy(); c[0, 0], c[0, 1] = a[0, 1], a[0, 0]                # same values, other order
+    assert ctx.tensor(c).checksum() != t1.checksum()
+    z = np.zeros((4, 4)); nz = z.copy(); nz[1, 1] = -0.0
+    assert ctx.tensor(z).checksum() != ctx.tensor(nz).checksum()    # bits, not values
+    assert ctx.empty(0, 5).checksum() == 0
+
+
 def test_linear_is_deterministic_run_to_run(ctx):
     rng = np.random.default_rng(0)
     X, W, b = rng.standard_normal((512, 300)), rng.standard_normal((200, 300)), rng.standard_normal((1, 200))
@@ -284,6 +352,18 @@ def test_argmax_first_maximum_wins(ctx, oc):
     assert rt.argmax(ctx.tensor(wide)).tolist() == oc.argmax(wide).tolist() == [77, 0, 0]
 
 
+@pytest.mark.parametrize("cols", [10, 100, 300, 1000, 2048, 3000])
+def test_xent_of_an_empty_batch_is_nan_like_the_reference(ctx, cols):
+    """Zero rows: `-(Σ t·ln p) / 0` is 0/0 = NaN in the reference (cross_entropy.rs:38) for
+    every class count; no launch may fail on the empty grid."""
+    logits, truth = ctx.empty(0, cols), ctx.empty(0, cols)
+    loss_fn = rt.CrossEntropyLoss()
+    loss = loss_fn.forward(logits, truth)
+    assert np.isnan(loss) and np.isnan(loss_fn.last_accuracy)
+    assert loss_fn.backward().shape == (0, cols)
+    ctx.check_device()
+
+
 def test_result_slot_misuse(ctx):
     loss, acc = C.c_double(), C.c_double()
     st = ctx._lib.rst_xent_result(ctx.handle, 10_000, C.byref(loss), C.byref(acc))
@@ -408,11 +488,15 @@ def test_graph_replay_reproduces_the_eager_step(ctx, oc):
         xd.upload(X[s * 8:(s + 1) * 8]); td.upload(T[s * 8:(s + 1) * 8])
         step(eager, 1)
         eager_losses.append(loss_fn.result(1)[0])
-    # capture on the second model: one eager warm-up step at lr 0 semantics is not needed
-    # because capture itself executes nothing; weights change only on replay
+    # Nothing is allocated from the driver while recording, so the same step runs once,
+    # unrecorded, directly before the capture; that run moves the weights, which are put
+    # back before the replays (recording itself executes nothing).
     xd.upload(X[:8]); td.upload(T[:8])
+    step(graphed, 2)
     with ctx.capture() as cap:
         step(graphed, 2)
+    for lin, (w, b) in zip([l for l in graphed.layers if isinstance(l, rt.Linear)], W):
+        lin.weight.upload(w); lin.bias.upload(b)
     losses = []
     for s in range(3):
         xd.upload(X[s * 8:(s + 1) * 8]); td.upload(T[s * 8:(s + 1) * 8])
@@ -422,6 +506,54 @@ def test_graph_replay_reproduces_the_eager_step(ctx, oc):
     for a, b in zip(eager.parameters(), graphed.parameters()):
         assert np.array_equal(a.parm.numpy(), b.parm.numpy())
     cap.graph.destroy()
+
+
+def test_graph_keeps_its_blocks_out_of_the_allocator():
+    """Nothing is allocated from the driver while recording; the blocks the recorded kernels
+    address stay out of the cache until the graph is destroyed, so a later tensor can never be
+    handed memory that a replay overwrites."""
+    c = rt.Context(0)
+    try:
+        x = c.tensor(np.full((64, 64), 2.0))
+
+        def work():
+            a = c.empty(64, 64)                       # an intermediate: written, read, dropped
+            c._check(c._lib.rst_relu_forward(c.handle, x.handle, a.handle))
+            out = c.empty(64, 64)
+            c._check(c._lib.rst_relu_forward(c.handle, a.handle, out.handle))
+            return a.data_ptr(), out
+
+        # recording without a warm cache: no driver allocation is made, the call fails cleanly
+        c.empty_cache()
+        with pytest.raises(rt.RstError) as e:
+            with c.capture():
+                work()
+        assert e.value.status == _lib.RST_ERR_STATE and "directly before" in str(e.value)
+        # the unrecorded run fills the cache, the recorded one is served from it
+        _, out = work()
+        del out
+        allocs = c.memory_stats()["driver_allocs"]
+        with c.capture() as cap:
+            a_ptr, out = work()
+        assert c.memory_stats()["driver_allocs"] == allocs
+        out_ptr = out.data_ptr()
+        # while the graph lives neither block is handed out again, even after `out` is dropped
+        del out
+        later = [c.empty(64, 64) for _ in range(6)]
+        assert a_ptr not in {t.data_ptr() for t in later} and out_ptr not in {t.data_ptr() for t in later}
+        for t in later:
+            t.fill(-1.0)
+        cap.graph.launch()
+        c.synchronize()
+        for t in later:
+            assert np.array_equal(t.numpy(), np.full((64, 64), -1.0))     # the replay wrote elsewhere
+        in_use = c.memory_stats()["in_use"]
+        cap.graph.destroy()
+        assert c.memory_stats()["in_use"] == in_use - 2 * 64 * 64 * 8      # both blocks are back in the cache
+        again = {c.empty(64, 64).data_ptr() for _ in range(1)}
+        assert again & {a_ptr, out_ptr}
+    finally:
+        c.close()
 
 
 @pytest.mark.parametrize("B,cin,cout,fused_copy", [

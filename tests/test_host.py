@@ -141,3 +141,57 @@ def test_idx_reader_and_mnist_dataset(tmp_path):
         f.write(open(tmp_path / "train-images-idx3-ubyte", "rb").read()[:1000])
     with pytest.raises(ValueError):
         mnist.read_image_file(str(tmp_path / "short"))
+
+
+def test_default_initialiser_gives_every_layer_its_own_stream():
+    """The reference draws every layer from the thread generator (he.rs:13): layers built
+    without an initialiser must not share weights, whatever their shapes."""
+    from rstorch_b200 import module
+    module.reset_default_init(0)
+    a, b = rt.Linear(100, 100), rt.Linear(100, 100)
+    assert not np.array_equal(a._host_weight, b._host_weight)
+    c, d = rt.Linear(784, 100), rt.Linear(100, 10)
+    # the underlying unit normals (weights rescaled by sqrt(fan-in)) share no prefix either
+    zc, zd = c._host_weight.reshape(-1) * np.sqrt(784.0), d._host_weight.reshape(-1) * np.sqrt(100.0)
+    assert not np.allclose(zc[:1000], zd[:1000])
+    # a model built in order in a fresh process reproduces the benchmark's seed-0 weights
+    module.reset_default_init(0)
+    dims = [784, 100, 100, 10]
+    layers = [rt.Linear(dims[l], dims[l + 1]) for l in range(3)]
+    for lin, (w, bias) in zip(layers, synth.mlp_weights(0, dims)):
+        assert np.array_equal(lin._host_weight, w) and np.array_equal(lin._host_bias, bias)
+
+
+def test_linear_without_bias_has_one_parameter_pair():
+    lin = rt.Linear.without_bias(4, 3)
+    assert lin._host_bias is None and not lin.has_bias and lin._host_weight.shape == (3, 4)
+    with pytest.raises(RuntimeError, match="before any backward"):
+        lin.parameters()
+
+
+def test_basic_model_follows_the_reference_step_order():
+    """model.rs:19-31 with stand-in parts: forward, loss.forward, loss.backward, backward, step."""
+    calls = []
+
+    class M(rt.Module):
+        def forward(self, x):
+            calls.append("module.forward"); return x
+
+        def backward(self, g):
+            calls.append("module.backward"); return g
+
+    class L(rt.Loss):
+        def forward(self, p, t):
+            calls.append("loss.forward"); return 0.0
+
+        def backward(self):
+            calls.append("loss.backward"); return None
+
+    class O(rt.Optimizer):
+        def step(self, module):
+            calls.append("optim.step")
+
+    model = rt.BasicModel.new(M(), L(), O())
+    model.step("x", "t")
+    assert calls == ["module.forward", "loss.forward", "loss.backward", "module.backward", "optim.step"]
+    assert model.predict("x") == "x" and calls[-1] == "module.forward"

@@ -184,3 +184,31 @@ def test_multistep_and_skip_first_dx_do_not_change_results(oc):
     for (wa, ba), (wb, bb) in zip(w1, w2):
         assert np.array_equal(wa, wb) and np.array_equal(ba, bb)
     assert 2.0 < l1[0] < 2.8          # ~ln(10) at initialisation
+
+
+def test_oracle_generator_matches_the_library_generator_bit_for_bit():
+    """The benchmark's CPU arm draws its inputs from the oracle's own generator; both
+    generators restate the same streams (splitmix64 words, 53-bit uniforms, Box-Muller)."""
+    from oracle import oracle_synth as osy
+    from rstorch_b200 import synth
+    for seed, purpose, index in [(0, "weight", 0), (3, "gaussian.x", 0), (7, "x", 5)]:
+        k = synth.stream_key(seed, purpose, index)
+        assert k == osy.stream_key(seed, purpose, index)
+        assert np.array_equal(synth.uniform(k, 5000, offset=123), osy.uniform(k, 5000, offset=123))
+        assert np.array_equal(synth.normal(k, 5000, std=0.02, mean=0.5, offset=99),
+                              osy.normal(k, 5000, std=0.02, mean=0.5, offset=99))
+    for a, b in zip(synth.mnist_like(0, 10, 64), osy.mnist_like(0, 10, 64)):
+        assert np.array_equal(a, b)
+    for a, b in zip(synth.gaussian_batch(0, 2, 16, 48, 24, 9, 128), osy.gaussian_batch(0, 2, 16, 48, 24, 9, 128)):
+        assert np.array_equal(a, b)
+    for (wa, ba), (wb, bb) in zip(synth.mlp_weights(0, [64, 48, 10]), osy.mlp_weights(0, [64, 48, 10])):
+        assert np.array_equal(wa, wb) and np.array_equal(ba, bb)
+
+
+def test_epoch_permutation_mirror_is_a_seeded_bijection():
+    for n in (1, 2, 3, 17, 256, 1000, 60000):
+        p = on.epoch_permutation(11, n)
+        assert np.array_equal(np.sort(p), np.arange(n))
+    a, b = on.epoch_permutation(1, 1000), on.epoch_permutation(2, 1000)
+    assert not np.array_equal(a, b) and np.array_equal(a, on.epoch_permutation(1, 1000))
+    assert (a != np.arange(1000)).mean() > 0.9          # far from the identity
