@@ -86,9 +86,6 @@ struct rst_ctx {
     int device;
     int num_sms;
     cudaStream_t compute, copy, comm;
-    cudaStream_t aux;         // second compute stream: the dW product of a large layer runs next to its dX product
-    cudaEvent_t aux_fork, aux_join;
-    bool overlap_dw;
     rst::CachingAllocator alloc;
     std::string last_error;
     uint64_t launches;
@@ -211,13 +208,9 @@ struct GemmArgs {
     double* colsum_out;       // optional [M]: Σ_k A(m,k) / divisor when A is M-major (db)
     double* C_transposed;     // optional [N,M]: a second, transposed copy of C (M-major A with N-major B
                               // and large tiles only; the caller checks gemm_writes_transposed)
-    cudaStream_t stream;      // nullptr = the context's compute stream
     long long wait_limit_cycles;  // 0 = the default bound of a barrier wait (about two seconds)
     bool starve_producer;     // self-test only: no tile is ever copied, every consumer wait runs out
 };
-// Whether launch_gemm would run this product with large tiles and without split K, i.e.
-// without touching the context's split-K workspace.
-bool gemm_is_large_unsplit(const rst_ctx* ctx, const GemmArgs& a);
 // Whether launch_gemm would honour C_transposed for this product.
 bool gemm_writes_transposed(const rst_ctx* ctx, const GemmArgs& a);
 // *colsum_done (optional) tells whether colsum_out was produced by the GEMM kernel itself.
@@ -228,7 +221,7 @@ int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done = nullptr);
 int launch_gemm_group(rst_ctx* ctx, const GemmArgs* args, int n, bool* grouped);
 
 int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols, double n,
-                      double* out, cudaStream_t stream = nullptr);
+                      double* out);
 int launch_relu_forward(rst_ctx* ctx, const double* x, double* y, int64_t n);
 int launch_relu_backward(rst_ctx* ctx, const double* dy, const double* xpre, double* dx,
                          int64_t n);

@@ -234,9 +234,8 @@ int launch_fill(rst_ctx* ctx, double* x, double v, int64_t n) {
 }
 
 int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols, double n,
-                      double* out, cudaStream_t stream) {
+                      double* out) {
     if (cols == 0) return RST_OK;
-    if (!stream) stream = ctx->compute;
     int64_t col_blocks = (cols + kColsPerBlock - 1) / kColsPerBlock;
     // enough row parts to fill the GPU about four times over, at least 64 rows each
     int64_t want_parts = ((int64_t)ctx->num_sms * 4 + col_blocks - 1) / col_blocks;
@@ -250,10 +249,10 @@ int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols
     size_t need = (size_t)parts * (size_t)cols * sizeof(double);
     RST_TRY(ensure_scratch(ctx, (void**)&ctx->colsum_ws, &ctx->colsum_ws_bytes, need, "column-sum"));
     dim3 g1((unsigned)col_blocks, (unsigned)parts);
-    colsum_pass1<<<g1, kThreads, 0, stream>>>(dY, rows, cols, rows_per, ctx->colsum_ws);
+    colsum_pass1<<<g1, kThreads, 0, ctx->compute>>>(dY, rows, cols, rows_per, ctx->colsum_ws);
     RST_TRY(after_launch(ctx, "colsum_pass1"));
     int g2 = (int)((cols + kThreads - 1) / kThreads);
-    colsum_pass2<<<g2, kThreads, 0, stream>>>(ctx->colsum_ws, (int)parts, cols, n, out);
+    colsum_pass2<<<g2, kThreads, 0, ctx->compute>>>(ctx->colsum_ws, (int)parts, cols, n, out);
     return after_launch(ctx, "colsum_pass2");
 }
 

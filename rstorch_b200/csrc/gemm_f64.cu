@@ -564,13 +564,12 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     }
     p.colsum_out = FUSE_COLSUM ? a.colsum_out : nullptr;
     dim3 grid((unsigned)(p.tiles_m * p.tiles_n), (unsigned)p.splits);
-    cudaStream_t stream = a.stream ? a.stream : ctx->compute;
-    launch_step_kernel(ctx, stream, kernel, grid, dim3(C_::kThreads), (size_t)C_::kSmemBytes, tmA, tmB, p);
+    launch_step_kernel(ctx, ctx->compute, kernel, grid, dim3(C_::kThreads), (size_t)C_::kSmemBytes, tmA, tmB, p);
     RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma"));
     if (p.splits > 1) {
         const long long total = a.M * a.N + (p.colsum_out ? a.M : 0);
         const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
-        launch_step_kernel(ctx, stream, splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, p);
+        launch_step_kernel(ctx, ctx->compute, splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, p);
         RST_TRY(after_launch(ctx, "splitk_reduce_kernel"));
     }
     return RST_OK;
@@ -639,15 +638,6 @@ int launch_layout(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, bool* colsum_d
 
 }  // namespace
 
-bool gemm_is_large_unsplit(const rst_ctx* ctx, const GemmArgs& a) {
-    if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.M > 0x7fffff00LL || a.N > 0x7fffff00LL || a.K > 0x7fffff00LL) return false;
-    const long long a_inner = a.a_kmajor ? a.K : a.M, b_inner = a.b_kmajor ? a.K : a.N;
-    if ((a_inner % 2) || (b_inner % 2) || ((((uintptr_t)a.A | (uintptr_t)a.B) & 15u) != 0)) return false;
-    const long long tiles_large = ((a.M + 127) / 128) * ((a.N + 127) / 128);
-    const long long k_tiles = (a.K + kBK - 1) / kBK;
-    return tiles_large >= ctx->num_sms && large_tile_splits(ctx, tiles_large, k_tiles) == 1;
-}
-
 bool gemm_writes_transposed(const rst_ctx* ctx, const GemmArgs& a) {
     if (a.a_kmajor || a.b_kmajor || !a.C_transposed) return false;
     if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.M > 0x7fffff00LL || a.N > 0x7fffff00LL || a.K > 0x7fffff00LL) return false;
@@ -689,7 +679,7 @@ int launch_gemm(rst_ctx* ctx, const GemmArgs& a, bool* colsum_done) {
         long long sbk = a.b_kmajor ? 1 : a.N, sbn = a.b_kmajor ? a.K : 1;
         long long total = a.M * a.N;
         int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
-        gemm_f64_plain<<<blocks, 256, 0, a.stream ? a.stream : ctx->compute>>>(a.A, a.B, sam, sak, sbk, sbn, p);
+        gemm_f64_plain<<<blocks, 256, 0, ctx->compute>>>(a.A, a.B, sam, sak, sbk, sbn, p);
         return after_launch(ctx, "gemm_f64_plain");
     }
     if (a.a_kmajor && a.b_kmajor) return launch_layout<true, true>(ctx, a, p, colsum_done);

@@ -95,10 +95,8 @@ GemmArgs weight_grad_args(const rst_tensor* dY, const rst_tensor* X, rst_tensor*
     return gw;
 }
 
-int weight_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X, rst_tensor* dW, rst_tensor* db,
-                cudaStream_t stream = nullptr) {
-    GemmArgs gw = weight_grad_args(dY, X, dW, db);
-    gw.stream = stream;
+int weight_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X, rst_tensor* dW, rst_tensor* db) {
+    const GemmArgs gw = weight_grad_args(dY, X, dW, db);
     bool db_done = false;
     {
         ProfScope prof(c, "gemm_dW");
@@ -106,44 +104,12 @@ int weight_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* X, rst_tenso
     }
     if (db && !db_done) {
         ProfScope prof(c, "colsum");
-        RST_TRY(launch_colsum_div(c, dY->data, X->rows, dY->cols, gw.divisor, db->data, stream));
+        RST_TRY(launch_colsum_div(c, dY->data, X->rows, dY->cols, gw.divisor, db->data));
     }
     return RST_OK;
 }
 
-// dW (with db) and dX of one layer both read dY and nothing of each other.  When both are
-// large-tile products the dW launches go to the context's second stream, between a fork
-// event (everything queued so far, dY included, is done) and a join event that the
-// compute stream waits for before the call returns: the two grids then share the GPU, the
-// CTAs of one filling the SMs that the last, partly empty wave of the other leaves idle
-// (4096 tiles on 148 SMs are 27.7 waves; two such grids together lose one partial wave
-// instead of two).  Every later launch on the compute stream is ordered after both, so
-// callers and the allocator see the same ordering as without the second stream.  Not
-// taken while a graph is recorded or kernel classes are being timed (the timing events
-// sit on the compute stream), nor when either product needs the split-K workspace.
-struct DwOverlap {
-    rst_ctx* c;
-    bool on;
-    DwOverlap(rst_ctx* ctx, const GemmArgs& gw, const GemmArgs* gx) : c(ctx), on(false) {
-        on = gx && c->overlap_dw && !c->capturing && !c->profiling && gemm_is_large_unsplit(c, gw) &&
-             gemm_is_large_unsplit(c, *gx);
-    }
-    int fork() {
-        if (!on) return RST_OK;
-        RST_CUDA(c, cudaEventRecord(c->aux_fork, c->compute));
-        RST_CUDA(c, cudaStreamWaitEvent(c->aux, c->aux_fork, 0));
-        return RST_OK;
-    }
-    int join() {
-        if (!on) return RST_OK;
-        RST_CUDA(c, cudaEventRecord(c->aux_join, c->aux));
-        RST_CUDA(c, cudaStreamWaitEvent(c->compute, c->aux_join, 0));
-        return RST_OK;
-    }
-    cudaStream_t stream() const { return on ? c->aux : nullptr; }
-};
-
-GemmArgs input_grad_args(const rst_tensor* dY, const rst_tensor* W, const rst_tensor* mask, rst_tensor* dX) {
+int input_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* W, const rst_tensor* mask, rst_tensor* dX) {
     GemmArgs gx{};
     gx.A = dY->data; gx.B = W->data; gx.C = dX->data;
     gx.M = dY->rows; gx.N = W->cols; gx.K = W->rows;
@@ -151,11 +117,6 @@ GemmArgs input_grad_args(const rst_tensor* dY, const rst_tensor* W, const rst_te
     gx.epilogue = mask ? kEpiMask : kEpiNone;
     gx.mask_src = mask ? mask->data : nullptr;
     gx.divisor = 1.0;
-    return gx;
-}
-
-int input_grad(rst_ctx* c, const rst_tensor* dY, const rst_tensor* W, const rst_tensor* mask, rst_tensor* dX) {
-    const GemmArgs gx = input_grad_args(dY, W, mask, dX);
     ProfScope prof(c, "gemm_dX");
     return launch_gemm(c, gx);
 }
@@ -167,13 +128,9 @@ extern "C" int rst_linear_backward(rst_ctx* c, const rst_tensor* dY, const rst_t
                                    rst_tensor* db, rst_tensor* dX) {
     RST_TRY(need_ctx(c));
     RST_TRY(check_linear_backward(c, dY, X, W, mask, dW, db, dX));
-    GemmArgs gx{};
-    if (dX) gx = input_grad_args(dY, W, mask, dX);
-    DwOverlap side(c, weight_grad_args(dY, X, dW, db), dX ? &gx : nullptr);
-    RST_TRY(side.fork());
-    RST_TRY(weight_grad(c, dY, X, dW, db, side.stream()));
+    RST_TRY(weight_grad(c, dY, X, dW, db));
     if (dX) RST_TRY(input_grad(c, dY, W, mask, dX));
-    return side.join();
+    return RST_OK;
 }
 
 extern "C" int rst_transpose(rst_ctx* c, const rst_tensor* src, rst_tensor* dst) {
@@ -211,25 +168,29 @@ extern "C" int rst_linear_backward_t(rst_ctx* c, const rst_tensor* dY, const rst
         if (dX_t->data == dX->data || dX_t->data == dY->data || dX_t->data == W->data)
             return fail(c, RST_ERR_INVALID_ARG, "Linear::backward: dX_t aliases another operand");
     }
-    if (!dX) return weight_grad(c, dY, X, dW, db);
-    GemmArgs gx = input_grad_args(dY, W, mask, dX);
-    bool fused_copy = false;
-    if (dY_t) {
-        gx.A = dY_t->data;                                          // dX[B,in] = (dYᵀ)ᵀ · W
-        gx.a_kmajor = false;
+    RST_TRY(weight_grad(c, dY, X, dW, db));
+    if (!dX) return RST_OK;
+    if (!dY_t) {
+        RST_TRY(input_grad(c, dY, W, mask, dX));
+    } else {
+        GemmArgs gx{};
+        gx.A = dY_t->data; gx.B = W->data; gx.C = dX->data;         // dX[B,in] = (dYᵀ)ᵀ · W
+        gx.M = dY->rows; gx.N = W->cols; gx.K = W->rows;
+        gx.a_kmajor = false; gx.b_kmajor = false;
+        gx.epilogue = mask ? kEpiMask : kEpiNone;
+        gx.mask_src = mask ? mask->data : nullptr;
+        gx.divisor = 1.0;
         gx.C_transposed = dX_t ? dX_t->data : nullptr;
-        fused_copy = dX_t && gemm_writes_transposed(c, gx);
+        const bool fused_copy = dX_t && gemm_writes_transposed(c, gx);
         if (!fused_copy) gx.C_transposed = nullptr;
+        {
+            ProfScope prof(c, "gemm_dX");
+            RST_TRY(launch_gemm(c, gx));
+        }
+        if (!dX_t || fused_copy) return RST_OK;
     }
-    DwOverlap side(c, weight_grad_args(dY, X, dW, db), &gx);
-    RST_TRY(side.fork());
-    RST_TRY(weight_grad(c, dY, X, dW, db, side.stream()));
-    {
-        ProfScope prof(c, "gemm_dX");
-        RST_TRY(launch_gemm(c, gx));
-    }
-    if (dX_t && !fused_copy) RST_TRY(launch_transpose(c, dX->data, dX->rows, dX->cols, dX_t->data));
-    return side.join();
+    if (dX_t) RST_TRY(launch_transpose(c, dX->data, dX->rows, dX->cols, dX_t->data));
+    return RST_OK;
 }
 
 // Sequential::backward over n Linear layers (src/module/sequential.rs:88-94 folding

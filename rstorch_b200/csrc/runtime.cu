@@ -259,13 +259,7 @@ extern "C" int rst_ctx_create(int device, rst_ctx** out) {
     c->flush_buf = nullptr; c->flush_bytes = 0;
     c->encode_tiled = nullptr;
     c->d_status = nullptr; c->h_status = nullptr; c->d_results = nullptr; c->h_results = nullptr;
-    c->compute = c->copy = c->comm = c->aux = nullptr;
-    c->aux_fork = c->aux_join = nullptr;
-    {
-        // RSTORCH_B200_OVERLAP_DW=0 keeps every product of a backward pass on one stream (for A/B timing)
-        const char* v = std::getenv("RSTORCH_B200_OVERLAP_DW");
-        c->overlap_dw = !(v && v[0] == '0');
-    }
+    c->compute = c->copy = c->comm = nullptr;
     for (int i = 0; i < kXentSlots; ++i) { c->result_event[i] = nullptr; c->result_pending[i] = false; c->result_in_graph[i] = false; }
 
 #define CTX_CUDA(call)                                                                   \
@@ -280,9 +274,6 @@ extern "C" int rst_ctx_create(int device, rst_ctx** out) {
     } while (0)
 
     CTX_CUDA(cudaStreamCreateWithFlags(&c->compute, cudaStreamNonBlocking));
-    CTX_CUDA(cudaStreamCreateWithFlags(&c->aux, cudaStreamNonBlocking));
-    CTX_CUDA(cudaEventCreateWithFlags(&c->aux_fork, cudaEventDisableTiming));
-    CTX_CUDA(cudaEventCreateWithFlags(&c->aux_join, cudaEventDisableTiming));
     {
         // The collective's few CTAs must get an SM as soon as one frees up, ahead of the
         // thousands of queued CTAs of the GEMM it overlaps with: highest stream priority.
@@ -339,9 +330,6 @@ extern "C" int rst_ctx_destroy(rst_ctx* c) {
     if (c->splitk_ws) cudaFree(c->splitk_ws);
     if (c->colsum_ws) cudaFree(c->colsum_ws);
     if (c->flush_buf) cudaFree(c->flush_buf);
-    if (c->aux_fork) cudaEventDestroy(c->aux_fork);
-    if (c->aux_join) cudaEventDestroy(c->aux_join);
-    if (c->aux) cudaStreamDestroy(c->aux);
     if (c->compute) cudaStreamDestroy(c->compute);
     if (c->copy) cudaStreamDestroy(c->copy);
     if (c->comm) cudaStreamDestroy(c->comm);
@@ -354,7 +342,6 @@ extern "C" int rst_ctx_destroy(rst_ctx* c) {
 extern "C" int rst_ctx_synchronize(rst_ctx* c) {
     if (!valid(c)) return fail(nullptr, RST_ERR_INVALID_ARG, "not a live context");
     RST_CUDA(c, cudaStreamSynchronize(c->compute));
-    RST_CUDA(c, cudaStreamSynchronize(c->aux));
     RST_CUDA(c, cudaStreamSynchronize(c->copy));
     RST_CUDA(c, cudaStreamSynchronize(c->comm));
     return RST_OK;
