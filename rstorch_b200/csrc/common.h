@@ -91,6 +91,7 @@ struct rst_ctx {
     uint64_t launches;
     bool capturing;
     bool overlap_launches;    // programmatic dependent launch for the step's kernels
+    bool stream_tail;         // large GEMMs hand the last, partly filled wave out in equal k runs
 
     int* d_status;            // device status words (kernels report bounded-wait expiry)
     int* h_status;            // pinned mirror

@@ -45,7 +45,27 @@ struct GemmParams {
     int splits;
     int epilogue;
     int starve;             // self-test: the producer issues no copy, so every consumer wait runs out
+    // Tail of a product whose tile count is not a multiple of the SM count: the main launch
+    // computes tiles [0, sk_first_tile), one per CTA; the remaining tiles' k-tiles, laid end to
+    // end, are cut into equal runs of sk_units k-tiles for the sk_ctas CTAs of a second launch,
+    // which store raw partial tiles that streamk_fixup_kernel adds up in k order.  sk_ctas == 0:
+    // the main launch computes every tile (or split of a tile).
+    int sk_first_tile, sk_ctas, sk_units, sk_slots;
+    double* sk_ws;          // [sk_ctas][sk_slots][BM*BN]
 };
+
+// Output tile `tile_index` in launch order -> tile coordinates: groups of 8 tile rows share
+// their B tiles in L2.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile_index, int& tile_m, int& tile_n) {
+    constexpr int kGroup = 8;
+    const int tiles_per_group = kGroup * p.tiles_n;
+    const int group = tile_index / tiles_per_group;
+    const int first_m = group * kGroup;
+    const int group_rows = min(p.tiles_m - first_m, kGroup);
+    const int in_group = tile_index - group * tiles_per_group;
+    tile_m = first_m + in_group % group_rows;
+    tile_n = in_group / group_rows;
+}
 
 __device__ __forceinline__ double apply_epilogue(const GemmParams& p, double v, long long r, long long c) {
     switch (p.epilogue) {
@@ -126,7 +146,7 @@ struct Cfg {
 // k range of split `split`.  tmA and tmB must refer to kernel parameters declared
 // __grid_constant__ (the TMA unit reads the descriptors through their address).
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM,
-          bool WRITE_T = false>
+          bool WRITE_T = false, bool STREAMED = false>
 __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                                           const int tile_index, const int split) {
     using C_ = Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
@@ -140,18 +160,37 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // tile coordinates: groups of 8 tile rows share their B tiles in L2
-    constexpr int kGroup = 8;
-    const int tiles_per_group = kGroup * p.tiles_n;
-    const int group = tile_index / tiles_per_group;
-    const int first_m = group * kGroup;
-    const int group_rows = min(p.tiles_m - first_m, kGroup);
-    const int in_group = tile_index - group * tiles_per_group;
-    const int tile_m = first_m + in_group % group_rows;
-    const int tile_n = in_group / group_rows;
-    const int m0 = tile_m * BM, n0 = tile_n * BN;
-    const int kt_begin = split * p.k_tiles_per_split;
-    const int kt_end = min(kt_begin + p.k_tiles_per_split, p.k_tiles);
+    // The work of this CTA is a short list of segments (tile, k range): one for a CTA that owns
+    // a tile (or a split of it), up to sk_slots for a CTA of the streamed tail.  The producer
+    // and the consumers walk the same list; the stage ring runs on across segments.
+    // STREAMED is a kernel of its own (the tail launch): in the ordinary kernel the segment list
+    // has one entry and all of this folds away.
+    constexpr bool streamed = STREAMED;
+    // Segment number `seg` of this CTA, derived from scratch each time so that nothing but
+    // `seg` stays live across the main loop.  CTA x of the tail launch owns the run that starts
+    // at k-tile x * sk_units of the tail laid end to end (31 bits suffice, the host checks).
+    int seg = 0, seg_tile = 0, kt_begin = 0, kt_end = 0;
+    auto next_segment = [&]() -> bool {
+        if (!streamed) {
+            if (seg > 0) return false;
+            seg_tile = tile_index;
+            kt_begin = split * p.k_tiles_per_split;
+            kt_end = min(kt_begin + p.k_tiles_per_split, p.k_tiles);
+        } else {
+            const int tail_units = (p.tiles_m * p.tiles_n - p.sk_first_tile) * p.k_tiles;
+            const int u0 = tile_index * p.sk_units;
+            const int u1 = min(u0 + p.sk_units, tail_units);
+            const int t = u0 / p.k_tiles + seg;              // tile of the tail this segment lies in
+            const int lo = max(u0, t * p.k_tiles), hi = min(u1, (t + 1) * p.k_tiles);
+            if (lo >= hi) return false;
+            seg_tile = p.sk_first_tile + t;
+            kt_begin = lo - t * p.k_tiles;
+            kt_end = hi - t * p.k_tiles;
+        }
+        ++seg;
+        return true;
+    };
+    int tile_m = 0, tile_n = 0, m0 = 0, n0 = 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -174,12 +213,17 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmB);
             int it = 0;
-            for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+            bool alive = true;
+            while (alive && next_segment()) {
+              tile_coords(p, seg_tile, tile_m, tile_n);
+              m0 = tile_m * BM; n0 = tile_n * BN;
+              for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait_bounded(empty_bar(s), ph ^ 1u, p.wait_limit)) {
                     atomicExch(p.status, kDevBarrierTimeout);
                     atomicExch(p.status + 1, 1);
+                    alive = false;
                     break;
                 }
                 mbar_expect_tx(full_bar(s), C_::kStageBytes);
@@ -200,6 +244,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
                     for (int j = 0; j < BN / 16; ++j)
                         tma_load_2d(Bs + j * kBoxBytes, &tmB, n0 + j * 16, k0, full_bar(s));
                 }
+              }
             }
         }
         return;
@@ -210,20 +255,12 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
     const int g = lane >> 2, t = lane & 3;
 
     double acc[MT][NT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.0;
 
     // Column sums of the M-major A operand (db = Σ_rows dY / n, linear.rs:65-67): the
     // warps of the first tile column that hold the A fragments anyway add them up.
     static_assert(!FUSE_COLSUM || !A_K, "column sums are taken from an M-major A operand");
-    const bool do_colsum = FUSE_COLSUM && p.colsum_out != nullptr && tile_n == 0 && wn == 0;
+    bool do_colsum = false;
     double asum[FUSE_COLSUM ? MT : 1][2];
-#pragma unroll
-    for (int mt = 0; mt < (FUSE_COLSUM ? MT : 1); ++mt) asum[mt][0] = asum[mt][1] = 0.0;
 
     // Per-thread byte offsets inside a stage that do not depend on the k sub-step.
     // K-major operand: row*128, chunk (2t+i) ^ (row%8) with row%8 == g.
@@ -306,8 +343,21 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
     auto stage_a = [&](int it) { return smem_base + (uint32_t)(it % STAGES) * C_::kStageBytes; };
 
     bool ok = true;
-    const int n_it = kt_end - kt_begin;
-    for (int it = 0; it < n_it; ++it) {
+    int it = 0;                           // stages consumed so far, over all segments
+  while (ok && next_segment()) {
+    tile_coords(p, seg_tile, tile_m, tile_n);
+    m0 = tile_m * BM; n0 = tile_n * BN;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.0;
+    do_colsum = FUSE_COLSUM && p.colsum_out != nullptr && tile_n == 0 && wn == 0;
+#pragma unroll
+    for (int mt = 0; mt < (FUSE_COLSUM ? MT : 1); ++mt) asum[mt][0] = asum[mt][1] = 0.0;
+
+    for (const int it_end = it + (kt_end - kt_begin); it < it_end; ++it) {
         if (!wait_full(it)) { ok = false; break; }
         const uint32_t As = stage_a(it);
 #pragma unroll
@@ -343,6 +393,24 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
     }
 
     const long long MN = p.M * p.N;
+    if (streamed) {
+        // raw partial tile, addressed inside the tile; the fix-up kernel adds the runs of a
+        // tile in k order and applies the epilogue
+        double* part = p.sk_ws + ((long long)tile_index * p.sk_slots + (seg - 1)) * (BM * BN);
+        if (ok) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int r = (int)(row_of(mt, h) - m0);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) part[r * BN + (int)(col_of(nt, e) - n0)] = acc[mt][nt][2 * h + e];
+                }
+        }
+        continue;
+    }
     if (p.splits == 1) {
         constexpr int kRun = B_K ? 2 : 4;
         const bool vec_ok = (p.N % kRun == 0) &&
@@ -405,7 +473,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
                 }
             }
         }
-        return;
+        continue;
     }
 
     // Split-K: every split stores its raw partial tile (and partial column sums);
@@ -429,6 +497,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
                 if (do_colsum && t == 0) colpart[(long long)split * p.M + r] = asum[mt][h];
             }
         }
+  }   // segments
 }
 
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM,
@@ -438,6 +507,16 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                   const GemmParams p) {
     gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM, WRITE_T>(tmA, tmB, p, (int)blockIdx.x,
                                                                                (int)blockIdx.y);
+}
+
+// The tail of a large product (see GemmParams::sk_*): CTA x computes the run of k-tiles
+// [x * sk_units, (x+1) * sk_units) of the tail's tiles laid end to end and stores one raw
+// partial tile per tile it touches.
+template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
+__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+gemm_f64_tma_dmma_tail(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const GemmParams p) {
+    gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, false, false, true>(tmA, tmB, p, (int)blockIdx.x, 0);
 }
 
 // Several independent products of one layout in one launch: the dW (and db) products of
@@ -496,6 +575,35 @@ __global__ void __launch_bounds__(256) splitk_reduce_grouped_kernel(const __grid
     grid_dependency_wait();
     for (int i = 0; i < gp.count; ++i)
         if (gp.p[i].splits > 1) reduce_splits(gp.p[i]);
+}
+
+// Adds up the partial tiles of the streamed tail.  Tile `tr` of the tail owns k-tiles
+// [tr*k_tiles, (tr+1)*k_tiles) of the tail's run; the CTAs whose runs of sk_units k-tiles
+// overlap it each left one partial tile, which are added in k order before the epilogue.
+// One block finishes 16 rows of a tile.
+template <int BM, int BN>
+__global__ void __launch_bounds__(256) streamk_fixup_kernel(const GemmParams p) {
+    grid_dependency_release();
+    grid_dependency_wait();
+    constexpr int kRowBlocks = BM / 16;
+    const int tr = (int)blockIdx.x / kRowBlocks, rb = (int)blockIdx.x % kRowBlocks;
+    int tile_m, tile_n;
+    tile_coords(p, p.sk_first_tile + tr, tile_m, tile_n);
+    const long long u_lo = (long long)tr * p.k_tiles, u_hi = u_lo + p.k_tiles - 1;
+    const int j_lo = (int)(u_lo / p.sk_units), j_hi = (int)(u_hi / p.sk_units);
+    for (int e = threadIdx.x; e < 16 * BN; e += 256) {
+        const int lr = rb * 16 + e / BN, lc = e % BN;
+        const long long r = (long long)tile_m * BM + lr, c = (long long)tile_n * BN + lc;
+        if (r >= p.M || c >= p.N) continue;
+        double v = 0.0;
+        for (int j = j_lo; j <= j_hi; ++j) {
+            const int slot = tr - (int)(((long long)j * p.sk_units) / p.k_tiles);   // the run's first tile is its slot 0
+            v += p.sk_ws[((long long)j * p.sk_slots + slot) * (BM * BN) + lr * BN + lc];
+        }
+        v = apply_epilogue(p, v, r, c);
+        p.C[r * p.N + c] = v;
+        if (p.Ct != nullptr) p.Ct[c * p.M + r] = v;
+    }
 }
 
 // Plain-load kernel for operands TMA cannot address (odd row pitch or a base
@@ -563,9 +671,39 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
         p.splitk_ws = ctx->splitk_ws;
     }
     p.colsum_out = FUSE_COLSUM ? a.colsum_out : nullptr;
-    dim3 grid((unsigned)(p.tiles_m * p.tiles_n), (unsigned)p.splits);
+    // A large product whose tiles do not fill the last wave (4096 tiles on 148 SMs: 27.7 waves,
+    // the last one two thirds full) hands the k-tiles of that wave's tiles out in equal runs,
+    // one per SM, so that all SMs finish together; a fix-up kernel adds the runs of a tile.
+    long long ctas_x = (long long)p.tiles_m * p.tiles_n;
+    p.sk_ctas = 0;
+    if (BM == 128 && !FUSE_COLSUM && p.splits == 1 && ctx->stream_tail && !a.starve_producer) {
+        const long long tiles = ctas_x, rest = tiles % ctx->num_sms;
+        const long long units = (rest * p.k_tiles + ctx->num_sms - 1) / ctx->num_sms;
+        if (tiles >= 2LL * ctx->num_sms && rest > 0 && rest * 10 < (long long)ctx->num_sms * 9 && units >= 16 &&
+            (rest + 1) * p.k_tiles < 0x7fffffffLL) {
+            p.sk_first_tile = (int)(tiles - rest);
+            p.sk_ctas = ctx->num_sms;
+            p.sk_units = (int)units;
+            p.sk_slots = (int)((units + p.k_tiles - 1) / p.k_tiles) + 1;
+            size_t need = (size_t)p.sk_ctas * (size_t)p.sk_slots * (size_t)(BM * BN) * sizeof(double);
+            RST_TRY(ensure_scratch(ctx, (void**)&ctx->splitk_ws, &ctx->splitk_ws_bytes, need, "tail-run"));
+            p.sk_ws = ctx->splitk_ws;
+            ctas_x = p.sk_first_tile;
+        }
+    }
+    dim3 grid((unsigned)ctas_x, (unsigned)p.splits);
     launch_step_kernel(ctx, ctx->compute, kernel, grid, dim3(C_::kThreads), (size_t)C_::kSmemBytes, tmA, tmB, p);
     RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma"));
+    if (p.sk_ctas > 0) {
+        auto tail = gemm_f64_tma_dmma_tail<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>;
+        RST_TRY(allow_dynamic_smem(ctx, reinterpret_cast<const void*>(tail), C_::kSmemBytes));
+        launch_step_kernel(ctx, ctx->compute, tail, dim3((unsigned)p.sk_ctas), dim3(C_::kThreads),
+                           (size_t)C_::kSmemBytes, tmA, tmB, p);
+        RST_TRY(after_launch(ctx, "gemm_f64_tma_dmma_tail"));
+        const unsigned blocks = (unsigned)((p.tiles_m * p.tiles_n - p.sk_first_tile) * (BM / 16));
+        launch_step_kernel(ctx, ctx->compute, streamk_fixup_kernel<BM, BN>, dim3(blocks), dim3(256), 0, p);
+        RST_TRY(after_launch(ctx, "streamk_fixup_kernel"));
+    }
     if (p.splits > 1) {
         const long long total = a.M * a.N + (p.colsum_out ? a.M : 0);
         const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)ctx->num_sms * 8);
