@@ -170,19 +170,24 @@ int rst_transpose(rst_ctx* ctx, const rst_tensor* src, rst_tensor* dst);
 
 /* Bias gradient without any allocation: db[c] = (Σ_r dY[r,c]) / rows, the same
  * value rst_linear_backward writes to db.  This entry point has no counterpart in
- * the reference; it exists for hosts that cannot call cudaMalloc where they need
- * the result: inside a stream-capture region, in a step with a hard latency
- * budget (an allocation may synchronise the device), or when another allocator
- * owns all device memory and hands this library raw pointers only.
+ * the reference.  It is for hosts that may not call cudaMalloc at the point where
+ * they need the result: a serving process or framework whose own allocator has
+ * claimed the whole device and hands this library raw pointers only (a cudaMalloc
+ * from a second party would fail there, or eat into a budget it does not own), and
+ * a step function with a hard latency bound (cudaMalloc and cudaFree can
+ * synchronise the whole device, and the regular path grows its column-sum scratch
+ * from the driver whenever a wider layer comes along).
  *   - dY and db are raw device pointers of the GPU that is current on the calling
  *     thread; `stream` is a cudaStream_t of that GPU (NULL = default stream).
- *   - No context, no tensor handles, no cudaMalloc/cudaFree: the partial column
- *     sums go to a fixed 2 MiB array inside the library's device image, which
- *     every GPU that loads the library holds until the process exits.
+ *   - No context, no tensor handles, no cudaMalloc/cudaFree and no allocating
+ *     library call: the partial column sums go to a fixed 2 MiB array inside the
+ *     library's device image, which every GPU that loads the library holds until
+ *     the process exits.
  *   - cols may be at most RST_BIAS_GRAD_NOALLOC_MAX_COLS; larger requests fail
  *     with RST_ERR_UNSUPPORTED and a message naming the limit.
- *   - The first call on each device looks up the array's device address; make
- *     that first call outside any stream capture.
+ *   - The first call on each device looks up the array's device address (once per
+ *     device, with that device current); let that first call come before any
+ *     stream capture.
  *   - All calls share the one array and it keeps the previous call's contents
  *     (the kernels overwrite every entry they later read, so nothing needs
  *     clearing).  Two calls whose kernels overlap on the GPU (different streams)

@@ -10,6 +10,10 @@
 #include <cstring>
 #include <vector>
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
 extern "C" {
 
 // C[M,N] = A[M,K]·B[K,N]; row-major, dense.
@@ -118,7 +122,16 @@ void orc_gemm_strided(int64_t M, int64_t N, int64_t K, const double* A, int64_t 
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < total; ++i) C[i] = 0.0;
     if (M == 0 || N == 0 || K == 0) return;
-    std::vector<double> bpack((size_t)(KC * (NC + NR)));
+    // Packing buffers live across calls (one caller thread at a time): a fresh allocation of
+    // this size per call is an mmap plus its page faults, which costs more than the packing.
+    static std::vector<double> bpack, apack_all;
+    int threads = 1;
+#ifdef _OPENMP
+    threads = omp_get_max_threads();
+#endif
+    const size_t apack_size = (size_t)((MC + MR) * KC);
+    if (bpack.size() < (size_t)(KC * (NC + NR))) bpack.resize((size_t)(KC * (NC + NR)));
+    if (apack_all.size() < apack_size * (size_t)threads) apack_all.resize(apack_size * (size_t)threads);
     for (int64_t jc = 0; jc < N; jc += NC) {
         const int64_t nc = (N - jc < NC) ? N - jc : NC;
         const int64_t panels = (nc + NR - 1) / NR;
@@ -132,14 +145,18 @@ void orc_gemm_strided(int64_t M, int64_t N, int64_t K, const double* A, int64_t 
             const int64_t row_blocks = (M + MC - 1) / MC, col_chunks = (nc + NCT - 1) / NCT;
 #pragma omp parallel
             {
-                std::vector<double> apack((size_t)((MC + MR) * KC));
+                int me = 0;
+#ifdef _OPENMP
+                me = omp_get_thread_num();
+#endif
+                double* apack = apack_all.data() + apack_size * (size_t)me;
                 int64_t packed_block = -1;
 #pragma omp for collapse(2) schedule(dynamic, 1)
                 for (int64_t rb = 0; rb < row_blocks; ++rb)
                     for (int64_t cc = 0; cc < col_chunks; ++cc) {
                         const int64_t i0 = rb * MC, mc = (M - i0 < MC) ? M - i0 : MC;
                         if (packed_block != rb) {
-                            pack_a(A, sai, sak, i0, mc, pc, kc, apack.data());
+                            pack_a(A, sai, sak, i0, mc, pc, kc, apack);
                             packed_block = rb;
                         }
                         const int64_t jt = cc * NCT, jt_end = (jt + NCT < nc) ? jt + NCT : nc;
@@ -147,7 +164,7 @@ void orc_gemm_strided(int64_t M, int64_t N, int64_t K, const double* A, int64_t 
                             const int64_t nr = (nc - jr < NR) ? nc - jr : NR;
                             const double* bp = bpack.data() + (jr / NR) * kc * NR;
                             for (int64_t ir = 0; ir < mc; ir += MR)
-                                micro_kernel(kc, apack.data() + (ir / MR) * kc * MR, bp, C + (i0 + ir) * N + jc + jr, N,
+                                micro_kernel(kc, apack + (ir / MR) * kc * MR, bp, C + (i0 + ir) * N + jc + jr, N,
                                              (mc - ir < MR) ? mc - ir : MR, nr);
                         }
                     }

@@ -261,14 +261,13 @@ int launch_colsum_div(rst_ctx* ctx, const double* dY, int64_t rows, int64_t cols
 // ---------------------------------------------------------------------------
 // Bias gradient for callers that must not allocate.
 //
-// Some hosts of this library cannot call cudaMalloc at the point where they need
-// db: code running inside a stream-capture region (an allocation there fails or
-// invalidates the capture), a step function with a hard latency budget (cudaMalloc
-// may synchronise the whole device), or a process whose device memory is fully
-// owned by another allocator and handed out as raw pointers.  The regular path
-// grows its column-sum scratch from the driver on demand; this entry point uses a
-// fixed array that lives in the library's device image instead, so every GPU that
-// loads the library holds kNoAllocScratchDoubles * 8 bytes (2 MiB) until exit.
+// Some hosts of this library may not call cudaMalloc at the point where they need db: a
+// process whose device memory is wholly claimed by another allocator and handed out as raw
+// pointers (a second party's cudaMalloc fails there or takes memory it was never given), and
+// a step function with a hard latency bound (cudaMalloc and cudaFree may synchronise the
+// whole device).  The regular path grows its column-sum scratch from the driver on demand;
+// this entry point uses a fixed array that lives in the library's device image instead, so
+// every GPU that loads the library holds kNoAllocScratchDoubles * 8 bytes (2 MiB) until exit.
 // ---------------------------------------------------------------------------
 namespace rst {
 namespace {

@@ -129,7 +129,14 @@ template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B
 struct Cfg {
     static_assert(A_K || !B_K, "M-major A with K-major B is not used by Linear");
     static constexpr int kConsumerWarps = WARPS_M * WARPS_N;
-    static constexpr int kThreads = (kConsumerWarps + 1) * 32;
+    // With two warpgroups of consumers the producer gets a warpgroup of its own (one working
+    // warp, three that leave at once), so that the CTA can move registers from the producer's
+    // warpgroup to the consumers' (setmaxnreg works on whole warpgroups).  A CTA of 9 warps is
+    // allocated registers as if it had 12 anyway: 168 per thread.  After the move the
+    // consumers own 232 each and the producer's warpgroup 40: 256*232 + 128*40 = 64512.
+    static constexpr bool kRegSplit = (kConsumerWarps == 8) && (BM == 128);
+    static constexpr int kThreads = kRegSplit ? 384 : (kConsumerWarps + 1) * 32;
+    static constexpr int kConsumerRegs = 232, kProducerRegs = 40;
     static constexpr int WTM = BM / WARPS_M, WTN = BN / WARPS_N;
     static constexpr int MT = WTM / 16, NT = WTN / 8;
     static_assert(WTM % 16 == 0 && WTN % 16 == 0, "warp tile must be a multiple of 16x16");
@@ -207,9 +214,10 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
     grid_dependency_release();
     grid_dependency_wait();
 
-    if (warp == C_::kConsumerWarps) {
+    if (warp >= C_::kConsumerWarps) {
         // ---------------- producer warp: one lane drives TMA ----------------
-        if (lane == 0 && !p.starve) {
+        if (C_::kRegSplit) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C_::kProducerRegs));
+        if (warp == C_::kConsumerWarps && lane == 0 && !p.starve) {
             tma_prefetch_desc(&tmA);
             tma_prefetch_desc(&tmB);
             int it = 0;
@@ -251,6 +259,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
     }
 
     // ---------------- consumer warps ----------------
+    if (C_::kRegSplit) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C_::kConsumerRegs));
     const int wm = warp / WARPS_N, wn = warp % WARPS_N;
     const int g = lane >> 2, t = lane & 3;
 
@@ -402,11 +411,22 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int r = (int)(row_of(mt, h) - m0);
+                    double* prow = part + (int)(row_of(mt, h) - m0) * BN;
+                    // the same runs of consecutive columns as in the final store: 16- and 32-byte stores
+                    if (B_K) {
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
+                        for (int nt = 0; nt < NT; ++nt) {
+                            double v[2] = {acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]};
+                            store_run<2>(prow + (int)(col_of(nt, 0) - n0), v);
+                        }
+                    } else {
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) part[r * BN + (int)(col_of(nt, e) - n0)] = acc[mt][nt][2 * h + e];
+                        for (int nt = 0; nt < NT; nt += 2) {
+                            double v[4] = {acc[mt][nt][2 * h], acc[mt][nt + 1][2 * h], acc[mt][nt][2 * h + 1],
+                                           acc[mt][nt + 1][2 * h + 1]};
+                            store_run<4>(prow + (int)(col_of(nt, 0) - n0), v);
+                        }
+                    }
                 }
         }
         continue;
@@ -502,7 +522,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap& tmA, const CUtensor
 
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM,
           bool WRITE_T = false>
-__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+__global__ void __launch_bounds__((Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>::kThreads), 1)
 gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const GemmParams p) {
     gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, FUSE_COLSUM, WRITE_T>(tmA, tmB, p, (int)blockIdx.x,
@@ -513,7 +533,7 @@ gemm_f64_tma_dmma(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // [x * sk_units, (x+1) * sk_units) of the tail's tiles laid end to end and stores one raw
 // partial tile per tile it touches.
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K>
-__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+__global__ void __launch_bounds__((Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>::kThreads), 1)
 gemm_f64_tma_dmma_tail(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const GemmParams p) {
     gemm_tile<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K, false, false, true>(tmA, tmB, p, (int)blockIdx.x, 0);
@@ -532,7 +552,7 @@ struct GroupParams {
 };
 
 template <int BM, int BN, int WARPS_M, int WARPS_N, int STAGES, bool A_K, bool B_K, bool FUSE_COLSUM>
-__global__ void __launch_bounds__((WARPS_M * WARPS_N + 1) * 32, 1)
+__global__ void __launch_bounds__((Cfg<BM, BN, WARPS_M, WARPS_N, STAGES, A_K, B_K>::kThreads), 1)
 gemm_f64_tma_dmma_grouped(const __grid_constant__ GroupMaps maps, const __grid_constant__ GroupParams gp) {
     int i = 0;
     while (i + 1 < gp.count && (int)blockIdx.x >= gp.first_cta[i + 1]) ++i;
@@ -679,7 +699,11 @@ int launch_cfg(rst_ctx* ctx, const GemmArgs& a, GemmParams& p, int splits) {
     if (BM == 128 && !FUSE_COLSUM && p.splits == 1 && ctx->stream_tail && !a.starve_producer) {
         const long long tiles = ctas_x, rest = tiles % ctx->num_sms;
         const long long units = (rest * p.k_tiles + ctx->num_sms - 1) / ctx->num_sms;
-        if (tiles >= 2LL * ctx->num_sms && rest > 0 && rest * 10 < (long long)ctx->num_sms * 9 && units >= 16 &&
+        // what the tail launch saves, in k-tile times per SM: the idle share of the last wave; what
+        // it costs: a second prologue, two partial-tile stores per CTA and the fix-up, about 100 of
+        // them (measured: 8192x4096x4096 with 41 to save broke even, 8192^3 with 166 gained 0.6 %)
+        const long long saved = (ctx->num_sms - rest) * p.k_tiles / ctx->num_sms;
+        if (tiles >= 2LL * ctx->num_sms && rest > 0 && saved >= 100 && units >= 16 &&
             (rest + 1) * p.k_tiles < 0x7fffffffLL) {
             p.sk_first_tile = (int)(tiles - rest);
             p.sk_ctas = ctx->num_sms;

@@ -1,8 +1,9 @@
 """The allocation-free bias-gradient entry point against the regular one.
 
-`rst_bias_grad_noalloc` serves hosts that cannot call cudaMalloc where they need
-db (inside a stream capture, under a latency budget, or when another allocator
-owns the device memory): it works on raw device pointers and keeps its partial
+`rst_bias_grad_noalloc` serves hosts that may not call cudaMalloc where they need
+db (a process whose own allocator has claimed the whole device and hands out raw
+pointers, or a step under a hard latency bound, which an allocation's device-wide
+synchronisation would break): it works on raw device pointers and keeps its partial
 sums in a fixed array inside the library instead of scratch grown on demand.
 This file is collected last on purpose, so a failure here cannot hide the result
 of any other test in a run that stops at the first failure.
