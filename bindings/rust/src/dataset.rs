@@ -65,6 +65,29 @@ impl DeviceDataset {
     pub fn gather_staged(&self, batch: usize, x: &Tensor, t: &Tensor) {
         self.ctx.check(unsafe { ffi::rst_dataset_gather_staged(self.h, batch as i64, x.raw(), t.raw()) });
     }
+
+    /// Draws the order of the next epoch on the device (`Shuffler::shuffle`,
+    /// src/data/dataset/shuffler.rs:22-25), seeded where the reference's `thread_rng` is not.
+    pub fn shuffle(&mut self, seed: u64) {
+        self.ctx.check(unsafe { ffi::rst_dataset_shuffle(self.h, seed) });
+    }
+
+    /// The batch of epoch positions `[first, first + batch)` (`Shuffler::get`, shuffler.rs:31-33).
+    #[must_use]
+    pub fn gather_epoch(&self, first: usize, batch: usize) -> (Tensor, Tensor) {
+        let x = self.ctx.empty(batch, self.features);
+        let t = self.ctx.empty(batch, self.classes);
+        self.ctx.check(unsafe { ffi::rst_dataset_gather_epoch(self.h, first as i64, batch as i64, x.raw(), t.raw()) });
+        (x, t)
+    }
+
+    /// The current epoch's order of the samples (identity before the first shuffle).
+    #[must_use]
+    pub fn epoch_order(&self) -> Vec<i64> {
+        let mut order = vec![0i64; self.len];
+        self.ctx.check(unsafe { ffi::rst_dataset_epoch_order(self.h, order.as_mut_ptr()) });
+        order
+    }
 }
 
 impl Drop for DeviceDataset {

@@ -29,6 +29,7 @@ pub mod dataset;
 pub mod ffi;
 pub mod graph;
 pub mod loss;
+pub mod model;
 pub mod module;
 pub mod optim;
 pub mod parallel;
@@ -38,6 +39,7 @@ pub mod utils;
 pub use dataset::DeviceDataset;
 pub use graph::Graph;
 pub use loss::CrossEntropyLoss;
+pub use model::BasicModel;
 pub use module::{Identity, Linear, ReLU, Sequential, Softmax};
 pub use optim::SGD;
 pub use tensor::{Context, Tensor};

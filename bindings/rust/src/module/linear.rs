@@ -36,6 +36,21 @@ impl Linear {
         Linear::new_with_kernel(input_size, output_size, KaimingNormal)
     }
 
+    /// A layer whose `bias` is `None`: the reference's struct holds `Option<Array2<f64>>` and
+    /// branches on it (linear.rs:51-53, 65-67, 74-77) although its public constructors always
+    /// fill it (:27).  `y = x·Wᵀ`, no `db`, one parameter pair.
+    #[must_use]
+    pub fn without_bias<I: InitParameters>(input_size: usize, output_size: usize, init: I) -> Linear {
+        let ctx = Context::current();
+        Linear {
+            weight: ctx.tensor(&init.weight(input_size, output_size)),
+            bias: None,
+            prev_input: None,
+            grad_weight: None,
+            grad_bias: None,
+        }
+    }
+
     /// Host copies, for tests and checkpoints.
     #[must_use]
     pub fn weight(&self) -> &Tensor {
