@@ -546,16 +546,19 @@ def run_mlp_workload(env: Env, wl: str, steps: int, warmup: int, batch: int = 0,
     # overlaps the previous step); small ones inline, where a thread hand-over would cost
     # more than the copy.
     prefetch = input_bytes >= (1 << 20)
-    e2e_warm = 2 * E2E_SLOTS
+    # three slots keep batch k (compute), k+1 (copy) and k+2 (assembly) in flight; batches that
+    # take longer to assemble than to train on get more slots, i.e. more assembling threads
+    slots = E2E_SLOTS if (not prefetch or input_bytes >= (256 << 20)) else 2 * E2E_SLOTS
+    e2e_warm = 2 * slots
     ds = rt.ArrayDataset(ds_x, ds_t)
     loader = rt.DataLoader(ds, rows, False, CyclingSampler(len(ds), rows * (steps + e2e_warm)), ctx,
-                           slots=E2E_SLOTS, prefetch=prefetch)
+                           slots=slots, prefetch=prefetch)
     e2e_graphs: dict[int, object] = {}
     batches = loader.iter_array()
 
     def e2e_step(k):
         x, t = next(batches)                      # batch k: assembled, copied, handed out by the loader
-        slot = k % E2E_SLOTS
+        slot = k % slots
         if slot in e2e_graphs:
             e2e_graphs[slot].launch()             # the step on this slot's device tensors, replayed
         else:
@@ -664,7 +667,7 @@ def run_mlp_workload(env: Env, wl: str, steps: int, warmup: int, batch: int = 0,
         "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": input_bytes,
                 "d2h_bytes_per_step": 32, "ms_per_step": e2e_ms / steps,
                 "host_assembly": "inside the timed region: DataLoader.iter_array gathers every batch's rows "
-                                 "into a pinned slot (" + ("helper thread, overlapping the previous step"
+                                 "into a pinned slot (" + (f"{slots - 2} helper thread(s), overlapping earlier steps"
                                                           if prefetch else "inline") + ")"},
         "gpu_launches": int(launches),
         "clocks": clocks,

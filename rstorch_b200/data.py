@@ -170,30 +170,39 @@ class DataLoader:
         self.ctx._check(self.ctx._lib.rst_stager_submit(self._stager, slot))
 
     def _iter_prefetched(self, order: np.ndarray) -> Iterator[tuple[Tensor, Tensor]]:
-        """Host assembly of batch k+2 (helper thread), the host-to-device copy of batch k+1
-        (copy stream) and the caller's work on batch k overlap.  Only the main thread calls
-        the library; the helper thread touches the pinned host arrays alone."""
+        """While the caller works on batch k, the copy stream moves batch k+1 to the device and
+        helper threads gather the rows of batches k+2 .. k+slots-1 into their pinned slots
+        (one thread per batch; numpy's `take` runs without the interpreter lock).  Only the main
+        thread calls the library; the helpers touch the pinned host arrays alone.  With two
+        slots nothing can be assembled ahead and the batches are built one by one."""
         import concurrent.futures as cf
         b, S, lib = self.batch_size, self._slots, self.ctx._lib
         n_batches = len(order) // b
         if n_batches == 0:
             return
-        with cf.ThreadPoolExecutor(max_workers=1) as pool:
-            def start(k):
-                # rst_stager_host waits until the previous copy out of this pinned slot is done
-                return pool.submit(self._assemble, self._host_views(k % S), order[k * b:(k + 1) * b])
+        with cf.ThreadPoolExecutor(max_workers=max(1, S - 2)) as pool:
+            pending: dict[int, cf.Future] = {}
+            started = 0
 
-            pending = {k: start(k) for k in range(min(2, n_batches, S))}
+            def start_up_to(last: int) -> None:
+                # rst_stager_host waits until the previous copy out of that pinned slot is done;
+                # batch j reuses the slot of batch j - S, whose copy was queued S - 1 batches ago
+                nonlocal started
+                while started <= min(last, n_batches - 1):
+                    pending[started] = pool.submit(self._assemble, self._host_views(started % S),
+                                                   order[started * b:(started + 1) * b])
+                    started += 1
+
+            start_up_to(max(1, S - 2))
             pending.pop(0).result()
             self.ctx._check(lib.rst_stager_submit(self._stager, 0))
             for k in range(n_batches):
                 if k + 1 < n_batches:
-                    if k + 1 not in pending:             # fewer than three slots: assembled only now
-                        pending[k + 1] = start(k + 1)
+                    start_up_to(k + 1)                   # only needed when fewer than three slots
                     pending.pop(k + 1).result()
                     self.ctx._check(lib.rst_stager_submit(self._stager, (k + 1) % S))
-                if k + 2 < n_batches and S >= 3:
-                    pending[k + 2] = start(k + 2)
+                if S >= 3:
+                    start_up_to(k + S - 1)
                 yield self._acquire(k % S)
 
     def _acquire(self, slot: int) -> tuple[Tensor, Tensor]:
