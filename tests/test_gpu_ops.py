@@ -92,8 +92,8 @@ LINEAR_SHAPES = [
     (2048, 1024, 2048), # 128x128 tiles, >= 148 of them
     (2048, 2048, 2048), # 256 large tiles = 1.73 waves: split K four ways in all three products
     (1920, 272, 1288),  # 128x128 tiles with ragged edges in M, N and K
-    (3000, 2100, 2500), # 480 / 408 / 340 large tiles, ragged everywhere: the last, partly filled wave of all
-                        # three products is handed out in k runs (tail launch + fix-up)
+    (3000, 4000, 4100), # 792 / 768 / 1056 large tiles, ragged everywhere, 188-257 k-tiles: the last, partly
+                        # filled wave of all three products is handed out in k runs (tail launch + fix-up)
 ]
 
 
@@ -560,7 +560,7 @@ def test_graph_keeps_its_blocks_out_of_the_allocator():
 
 @pytest.mark.parametrize("B,cin,cout,fused_copy", [
     (2048, 1280, 640, True),     # 160 large tiles, no split: dX and its transposed copy from one kernel
-    (3000, 2100, 2500, True),    # 408 large tiles: the transposed copy of the tail's tiles comes from the fix-up
+    (3000, 4000, 4100, True),    # 768 large tiles: the transposed copy of the tail's tiles comes from the fix-up
     (2048, 2048, 2048, False),   # 256 large tiles split K four ways: separate transpose kernel
     (96, 64, 40, False),         # small tiles
     (50, 33, 21, False),         # odd widths: plain-load kernel
