@@ -194,6 +194,32 @@ def test_tensor_checksum_tells_bit_patterns_apart(ctx):
     assert ctx.empty(0, 5).checksum() == 0
 
 
+def test_tail_launch_is_taken_and_agrees_with_whole_tiles(ctx, monkeypatch):
+    """3000 x 4100 x 4000 forward = 792 tiles of 128 x 128 = 5.35 waves on 148 SMs: the product
+    runs as main launch + tail launch + fix-up, and gives the sums of the whole-tile path in
+    another order (a context created with RSTORCH_B200_STREAM_TAIL=0 takes that path)."""
+    rng = np.random.default_rng(11)
+    X, W, b = rng.standard_normal((3000, 4000)), rng.standard_normal((4100, 4000)) / 64.0, rng.standard_normal((1, 4100))
+    lin = rt.Linear.new_with_kernel(4000, 4100, Fixed(W, b))
+    xd = ctx.tensor(X)
+    before = ctx.launch_count()
+    y = lin._forward(xd, fuse_relu=True).numpy()
+    sms = 148
+    expected = 3 if (792 % sms) and ((sms - 792 % sms) * 250 // sms >= 100) else 1
+    assert ctx.launch_count() - before == expected
+    monkeypatch.setenv("RSTORCH_B200_STREAM_TAIL", "0")
+    plain = rt.Context(0)
+    try:
+        lin2 = rt.Linear.new_with_kernel(4000, 4100, Fixed(W, b))
+        before = plain.launch_count()
+        y2 = lin2._forward(plain.tensor(X), fuse_relu=True).numpy()
+        assert plain.launch_count() - before == 1
+    finally:
+        plain.close()
+    assert rel_err(y, y2) < 1e-13 and np.array_equal(y == 0.0, y2 == 0.0)
+    ctx.check_device()
+
+
 def test_linear_is_deterministic_run_to_run(ctx):
     rng = np.random.default_rng(0)
     X, W, b = rng.standard_normal((512, 300)), rng.standard_normal((200, 300)), rng.standard_normal((1, 200))
