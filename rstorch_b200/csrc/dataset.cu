@@ -26,6 +26,7 @@ gather_normalize_onehot_kernel(const unsigned char* __restrict__ images, const u
                                const long long* __restrict__ indices, long long batch, int features, int classes,
                                double* __restrict__ X, double* __restrict__ T, long long n_samples,
                                int* __restrict__ status) {
+    __shared__ double value_table[kGatherThreads / 32][256];       // per warp: the normalised value of every u8
     grid_dependency_release();
     grid_dependency_wait();
     const int lane = threadIdx.x & 31;
@@ -45,12 +46,24 @@ gather_normalize_onehot_kernel(const unsigned char* __restrict__ images, const u
             continue;
         }
         const unsigned char* src = images + idx * features;
-        // pass 1: min and max of the sample by the ordering of u8 (utils.rs:11-12)
+        // pass 1: min and max of the sample by the ordering of u8 (utils.rs:11-12); four values
+        // per load where the row allows it
         unsigned int lo = 255u, hi = 0u;
-        for (int e = lane; e < features; e += 32) {
-            const unsigned int v = src[e];
-            lo = min(lo, v);
-            hi = max(hi, v);
+        const bool words = (features % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 3u) == 0);
+        if (words) {
+            const unsigned int* src4 = reinterpret_cast<const unsigned int*>(src);
+            for (int w = lane; w < features / 4; w += 32) {
+                const unsigned int q = src4[w];
+                const unsigned int b0 = q & 0xffu, b1 = (q >> 8) & 0xffu, b2 = (q >> 16) & 0xffu, b3 = q >> 24;
+                lo = min(min(lo, min(b0, b1)), min(b2, b3));
+                hi = max(max(hi, max(b0, b1)), max(b2, b3));
+            }
+        } else {
+            for (int e = lane; e < features; e += 32) {
+                const unsigned int v = src[e];
+                lo = min(lo, v);
+                hi = max(hi, v);
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -59,9 +72,28 @@ gather_normalize_onehot_kernel(const unsigned char* __restrict__ images, const u
         }
         const double dmin = (double)lo;
         const double range = (double)hi - dmin;                     // max - min in f64 (utils.rs:14)
+        // A sample holds at most 256 distinct values, so its `(f64(v) - min) / (max - min)` are
+        // computed once per value (the same subtraction and the same correctly rounded division
+        // as per element) and the elements are looked up: 256 divisions a sample instead of one
+        // per element, which is what bounded this kernel.
+        double* table = value_table[threadIdx.x >> 5];
+        __syncwarp();                                               // the previous sample's look-ups are done
+#pragma unroll
+        for (int j = 0; j < 8; ++j) table[lane + 32 * j] = ((double)(lane + 32 * j) - dmin) / range;
+        __syncwarp();
         // pass 2: normalise; lanes write consecutive doubles
         double* dst = X + b * features;
-        for (int e = lane; e < features; e += 32) dst[e] = ((double)src[e] - dmin) / range;
+        if (words && ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0)) {
+            const unsigned int* src4 = reinterpret_cast<const unsigned int*>(src);
+            for (int w = lane; w < features / 4; w += 32) {
+                const unsigned int q = src4[w];
+                double v[4] = {table[q & 0xffu], table[(q >> 8) & 0xffu], table[(q >> 16) & 0xffu], table[q >> 24]};
+                asm volatile("st.global.v4.f64 [%0], {%1,%2,%3,%4};" ::"l"(dst + 4 * w), "d"(v[0]), "d"(v[1]), "d"(v[2]),
+                             "d"(v[3]) : "memory");
+            }
+        } else {
+            for (int e = lane; e < features; e += 32) dst[e] = table[src[e]];
+        }
         const int label = labels[idx];
         double* trow = T + b * classes;
         for (int c = lane; c < classes; c += 32) trow[c] = (c == label) ? 1.0 : 0.0;
