@@ -324,10 +324,18 @@ int rst_comm_destroy(rst_comm* comm);
 int rst_allreduce_avg(rst_comm* comm, int n, rst_tensor* const* tensors);
 int rst_comm_join(rst_comm* comm);
 
-/* ---- whole-step replay ------------------------------------------------------
+/* ---- whole-step replay (no counterpart in the reference) ----------------------
  * Captures everything queued on the compute stream between begin and end into
  * a CUDA graph (configs whose step is a dozen short kernels are launch-bound).
- * Calls that block or allocate from the driver are not allowed in between. */
+ * Calls that block are not allowed in between, and nothing is allocated from the
+ * driver while recording: rst_tensor_alloc is served from the allocator's cache
+ * or fails with RST_ERR_STATE, so run the same step once, unrecorded, directly
+ * before every capture.  Every block the recorded kernels address (allocated or
+ * freed between begin and end) belongs to the graph from rst_graph_capture_end
+ * on: it stays out of the allocator, also after its tensor handle is freed,
+ * until rst_graph_destroy, so no later tensor is handed memory that a replay
+ * overwrites.  Tensors made before the capture (weights, inputs) must outlive
+ * the graph. */
 int rst_graph_capture_begin(rst_ctx* ctx);
 int rst_graph_capture_end(rst_ctx* ctx, rst_graph** out);
 int rst_graph_launch(rst_graph* g);
