@@ -130,6 +130,8 @@ class DataLoader:
         self._rng = np.random.default_rng(shuffle_seed)
         self._slots = int(slots)
         self._stager = None
+        self._views: dict = {}            # slot -> pinned host arrays
+        self._device_pairs: dict = {}     # slot -> wrappers of the slot's device tensors
 
     def __len__(self) -> int:
         return len(self.dataset) // self.batch_size
@@ -148,12 +150,20 @@ class DataLoader:
         return self._stager
 
     def _host_views(self, slot: int):
+        """The pinned arrays of a slot, once the previous copy out of them has finished.  The
+        arrays are made once per slot (the addresses never change); every call still goes
+        through rst_stager_host, which is what waits for that copy."""
         lib, ctx = self.ctx._lib, self.ctx
+        views = self._views.get(slot)
+        if views is not None:
+            ctx._check(lib.rst_stager_host(self._stager, slot, None, None))
+            return views
         px, pt = C.POINTER(C.c_double)(), C.POINTER(C.c_double)()
         ctx._check(lib.rst_stager_host(self._stager, slot, C.byref(px), C.byref(pt)))
         b = self.batch_size
         x = np.ctypeslib.as_array(px, shape=(b, self.dataset.samples.shape[1]))
         t = np.ctypeslib.as_array(pt, shape=(b, self.dataset.targets.shape[1]))
+        self._views[slot] = (x, t)
         return x, t
 
     def _assemble(self, views, indices: np.ndarray) -> None:
@@ -209,10 +219,14 @@ class DataLoader:
         lib, ctx = self.ctx._lib, self.ctx
         hx, ht = C.c_void_p(), C.c_void_p()
         ctx._check(lib.rst_stager_acquire(self._stager, slot, C.byref(hx), C.byref(ht)))
-        b = self.batch_size
-        # the stager owns these tensors; the wrappers must not free them
-        return (Tensor(ctx, hx, b, self.dataset.samples.shape[1], owns=False),
-                Tensor(ctx, ht, b, self.dataset.targets.shape[1], owns=False))
+        pair = self._device_pairs.get(slot)
+        if pair is None or pair[0].handle.value != hx.value:
+            b = self.batch_size
+            # the stager owns these tensors; the wrappers must not free them
+            pair = (Tensor(ctx, hx, b, self.dataset.samples.shape[1], owns=False),
+                    Tensor(ctx, ht, b, self.dataset.targets.shape[1], owns=False))
+            self._device_pairs[slot] = pair
+        return pair
 
     def _iter_device(self, order: np.ndarray) -> Iterator[tuple[Tensor, Tensor]]:
         """Batches of a DeviceDataset: the gather kernel writes into a small ring of
@@ -281,6 +295,7 @@ class DataLoader:
         if self._stager is not None and self.ctx.handle.value:
             self.ctx._lib.rst_stager_destroy(self._stager)
         self._stager = None
+        self._views, self._device_pairs = {}, {}
 
     def __del__(self):
         try:
