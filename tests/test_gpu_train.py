@@ -175,26 +175,28 @@ def test_wide_layer_sampled_entries_at_benchmark_size(ctx):
     ctx.check_device()
 
 
-def test_wide_mlp_full_size_step(ctx, oc):
-    """The wide-MLP workload at its own size (1024-4096-4096-4096-1000, batch 8192): one
-    whole step against the CPU restatement, every gradient and updated weight."""
-    dims, batch = [1024, 4096, 4096, 4096, 1000], 8192
+def test_wide_mlp_full_size_steps(ctx, oc):
+    """The wide-MLP workload at its own size (1024-4096-4096-4096-1000, batch 8192, a fresh
+    batch per step): three free-running steps against the CPU restatement, every gradient
+    and updated weight at every step."""
+    dims, batch, steps = [1024, 4096, 4096, 4096, 1000], 8192, 3
     w_cpu = [(w.copy(), b.copy()) for w, b in synth.mlp_weights(0, dims)]
     model = build_mlp(ctx, dims, w_cpu, identity=False)
-    X, T = synth.gaussian_batch(0, 0, 0, batch, dims[0], dims[-1], batch)
     loss_fn, opt = rt.CrossEntropyLoss(), rt.SGD.new(0.01)
-    pred = model.forward(ctx.tensor(X))
-    loss = loss_fn.forward(pred, ctx.tensor(T))
-    model.backward(loss_fn.backward(), need_input_grad=False)
-    opt.step(model)
-    losses, accs, grads = oc.mlp_train(dims, w_cpu, X, T, batch, 1, 0.01, skip_first_dx=True)
-    assert abs(loss - losses[0]) <= REL_TOL * abs(losses[0])
-    assert loss_fn.last_accuracy == accs[0]
-    for l, lin in enumerate(linears(model)):
-        assert rel_err(lin.grad_weight.numpy(), grads[l][0]) < REL_TOL, l
-        assert rel_err(lin.grad_bias.numpy(), grads[l][1]) < REL_TOL, l
-        assert rel_err(lin.weight.numpy(), w_cpu[l][0]) < REL_TOL, l
-        assert rel_err(lin.bias.numpy(), w_cpu[l][1]) < REL_TOL, l
+    for s in range(steps):
+        X, T = synth.gaussian_batch(0, s, 0, batch, dims[0], dims[-1], batch)
+        pred = model.forward(ctx.tensor(X))
+        loss = loss_fn.forward(pred, ctx.tensor(T))
+        model.backward(loss_fn.backward(), need_input_grad=False)
+        opt.step(model)
+        losses, accs, grads = oc.mlp_train(dims, w_cpu, X, T, batch, 1, 0.01, skip_first_dx=True)
+        assert abs(loss - losses[0]) <= REL_TOL * abs(losses[0]), s
+        assert loss_fn.last_accuracy == accs[0], s
+        for l, lin in enumerate(linears(model)):
+            assert rel_err(lin.grad_weight.numpy(), grads[l][0]) < REL_TOL, (s, l)
+            assert rel_err(lin.grad_bias.numpy(), grads[l][1]) < REL_TOL, (s, l)
+            assert rel_err(lin.weight.numpy(), w_cpu[l][0]) < REL_TOL, (s, l)
+            assert rel_err(lin.bias.numpy(), w_cpu[l][1]) < REL_TOL, (s, l)
     ctx.check_device()
 
 
