@@ -378,6 +378,8 @@ def verify_benched_shapes(env: Env, model, x_resident, samples: int = 64) -> dic
     W = lin.weight.numpy()
     b = lin.bias.numpy().reshape(-1)
     ld = np.longdouble
+    # ranks that exchange shares of the global-batch gradient divide by all ranks' rows
+    grad_rows = rows * (env.world if (env.comm is not None and getattr(env.comm, "shares", False)) else 1)
     rng = np.random.default_rng(1234 + env.rank)
 
     def row(t, r):                                    # row r of a device matrix, 8·cols bytes over the bus
@@ -395,7 +397,7 @@ def verify_benched_shapes(env: Env, model, x_resident, samples: int = 64) -> dic
         want_dx = float(np.dot(dy_r.astype(ld), W[:, k].astype(ld))) * (1.0 if x_r[k] > 0.0 else 0.0)
         got_dx = float(row(dX, r)[k])
         dxt_equal = dxt_equal and float(row(dXt, k)[r]) == got_dx
-        want_dw = float(np.dot(row(dYt, c).astype(ld), row(Xt, k).astype(ld)) / ld(rows))
+        want_dw = float(np.dot(row(dYt, c).astype(ld), row(Xt, k).astype(ld)) / ld(grad_rows))
         got_dw = float(row(dW, c)[k])
         for name, got, want in (("forward", got_y, want_y), ("dX", got_dx, want_dx), ("dW", got_dw, want_dw)):
             diffs[name].append(abs(got - want))
@@ -404,7 +406,7 @@ def verify_benched_shapes(env: Env, model, x_resident, samples: int = 64) -> dic
         err[name] = max(diffs[name]) / scale[name] if scale[name] > 0 else max(diffs[name])
     db_host = db.numpy().reshape(-1)
     cols = rng.integers(0, cout, size=8)
-    want_db = np.array([float(row(dYt, int(c)).astype(ld).sum() / ld(rows)) for c in cols])
+    want_db = np.array([float(row(dYt, int(c)).astype(ld).sum() / ld(grad_rows)) for c in cols])
     err["db"] = float(np.max(np.abs(db_host[cols] - want_db)) / max(np.max(np.abs(want_db)), 1e-300))
     ctx.check_device()
     return {"layer": f"Linear({cin}, {cout}) at {rows} rows", "sampled_entries_each": samples,

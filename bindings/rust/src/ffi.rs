@@ -134,6 +134,7 @@ extern "C" {
     pub fn rst_comm_destroy(comm: *mut rst_comm) -> c_int;
     pub fn rst_allreduce_avg(comm: *mut rst_comm, n: c_int, tensors: *const *mut rst_tensor) -> c_int;
     pub fn rst_comm_join(comm: *mut rst_comm) -> c_int;
+    pub fn rst_comm_share_gradients(comm: *mut rst_comm, on: c_int) -> c_int;
 
     // whole-step replay
     pub fn rst_graph_capture_begin(ctx: *mut rst_ctx) -> c_int;

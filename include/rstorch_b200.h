@@ -323,6 +323,15 @@ int rst_comm_create(rst_ctx* ctx, const void* id_bytes, int rank, int world, rst
 int rst_comm_destroy(rst_comm* comm);
 int rst_allreduce_avg(rst_comm* comm, int n, rst_tensor* const* tensors);
 int rst_comm_join(rst_comm* comm);
+/* Optional: exchange shares instead of averages.  With `on`, rst_linear_backward (and the
+ * chain and companion variants) on the communicator's context divide dW and db by
+ * rows(X)·world, so that every rank holds its share of the global-batch gradient
+ * dYᵀX / B, and rst_allreduce_avg adds the shares up with a plain sum, which NCCL may hand to
+ * the NVSwitch's in-network reduction (an average cannot go there: every rank's input would
+ * have to be scaled first).  After the exchange the tensors hold the same average as
+ * without the option: bit for bit when world is a power of two, to the last place otherwise.
+ * Between backward and exchange they hold 1/world of what linear.rs:63,66 computes. */
+int rst_comm_share_gradients(rst_comm* comm, int on);
 
 /* ---- whole-step replay (no counterpart in the reference) ----------------------
  * Captures everything queued on the compute stream between begin and end into

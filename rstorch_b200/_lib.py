@@ -103,6 +103,7 @@ _SIGNATURES = {
     "rst_comm_destroy": [P],
     "rst_allreduce_avg": [P, C.c_int, PP],
     "rst_comm_join": [P],
+    "rst_comm_share_gradients": [P, C.c_int],
     "rst_graph_capture_begin": [P],
     "rst_graph_capture_end": [P, PP],
     "rst_graph_launch": [P],

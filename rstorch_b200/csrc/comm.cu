@@ -76,6 +76,7 @@ struct rst_comm {
     cudaEvent_t ready;   // compute -> comm
     cudaEvent_t done;    // comm -> compute
     bool pending;
+    bool shares;         // gradients arrive divided by the global batch: the exchange sums them
 };
 
 static_assert(RST_COMM_ID_BYTES == sizeof(ncclUniqueId), "id size");
@@ -104,7 +105,7 @@ extern "C" int rst_comm_create(rst_ctx* c, const void* id_bytes, int rank, int w
     ncclComm_t comm = nullptr;
     int r = api.CommInitRank(&comm, world, id, rank);
     if (r != ncclSuccess) return fail(c, RST_ERR_NCCL, "ncclCommInitRank: %s", api.GetErrorString(r));
-    rst_comm* m = new rst_comm{c, comm, rank, world, nullptr, nullptr, false};
+    rst_comm* m = new rst_comm{c, comm, rank, world, nullptr, nullptr, false, false};
     if (cudaEventCreateWithFlags(&m->ready, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&m->done, cudaEventDisableTiming) != cudaSuccess) {
         api.CommDestroy(comm);
@@ -115,8 +116,23 @@ extern "C" int rst_comm_create(rst_ctx* c, const void* id_bytes, int rank, int w
     return RST_OK;
 }
 
+// With `on`, Linear::backward of the communicator's context divides dW and db by
+// rows(X) * world instead of rows(X): every rank then holds its share of the global-batch
+// gradient, and rst_allreduce_avg adds the shares up (a plain sum, which NCCL can hand to
+// the switch's in-network reduction; an average cannot go there because every rank's input
+// would have to be scaled first).  The result is the same average, bit for bit when the world
+// size is a power of two (dividing by 2^k commutes with rounding), to the last place otherwise.
+extern "C" int rst_comm_share_gradients(rst_comm* m, int on) {
+    if (!m || !valid(m->ctx)) return fail(nullptr, RST_ERR_INVALID_ARG, "bad communicator");
+    if (m->ctx->capturing) return fail(m->ctx, RST_ERR_STATE, "mode change during graph capture");
+    m->shares = on != 0;
+    m->ctx->grad_rows_scale = m->shares ? (double)m->world : 1.0;
+    return RST_OK;
+}
+
 extern "C" int rst_comm_destroy(rst_comm* m) {
     if (!m) return RST_OK;
+    if (valid(m->ctx) && m->shares) m->ctx->grad_rows_scale = 1.0;
     if (valid(m->ctx)) {
         cudaStreamSynchronize(m->ctx->comm);
         cudaStreamSynchronize(m->ctx->compute);
@@ -145,7 +161,8 @@ extern "C" int rst_allreduce_avg(rst_comm* m, int n, rst_tensor* const* tensors)
     for (int i = 0; i < n; ++i) {
         size_t count = (size_t)(tensors[i]->rows * tensors[i]->cols);
         if (count == 0) continue;
-        r = api.AllReduce(tensors[i]->data, tensors[i]->data, count, ncclFloat64, ncclAvg, m->comm, c->comm);
+        r = api.AllReduce(tensors[i]->data, tensors[i]->data, count, ncclFloat64, m->shares ? ncclSum : ncclAvg, m->comm,
+                          c->comm);
         if (r != ncclSuccess) {
             api.GroupEnd();
             return fail(c, RST_ERR_NCCL, "ncclAllReduce: %s", api.GetErrorString(r));

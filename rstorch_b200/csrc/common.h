@@ -92,6 +92,8 @@ struct rst_ctx {
     bool capturing;
     bool overlap_launches;    // programmatic dependent launch for the step's kernels
     bool stream_tail;         // large GEMMs hand the last, partly filled wave out in equal k runs
+    double grad_rows_scale;   // Linear::backward divides dW and db by rows(X) times this (1, or the world
+                              // size of a communicator that sums gradient shares instead of averaging)
 
     int* d_status;            // device status words (kernels report bounded-wait expiry)
     int* h_status;            // pinned mirror

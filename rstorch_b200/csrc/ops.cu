@@ -90,7 +90,9 @@ GemmArgs weight_grad_args(const rst_tensor* dY, const rst_tensor* X, rst_tensor*
     gw.A = dY->data; gw.B = X->data; gw.C = dW->data;
     gw.M = dY->cols; gw.N = X->cols; gw.K = X->rows;
     gw.a_kmajor = false; gw.b_kmajor = false;
-    gw.epilogue = kEpiDivN; gw.divisor = (double)X->rows;   // linear.rs:62
+    // n = rows(X) (linear.rs:62); times the world size when the ranks of a data-parallel run
+    // exchange shares of the global-batch gradient (rst_comm_share_gradients)
+    gw.epilogue = kEpiDivN; gw.divisor = (double)X->rows * X->ctx->grad_rows_scale;
     gw.colsum_out = db ? db->data : nullptr;
     return gw;
 }

@@ -257,6 +257,7 @@ extern "C" int rst_ctx_create(int device, rst_ctx** out) {
         const char* v = std::getenv("RSTORCH_B200_STREAM_TAIL");
         c->stream_tail = !(v && v[0] == '0');
     }
+    c->grad_rows_scale = 1.0;
     c->profiling = false;
     c->xent_partials = nullptr; c->xent_partials_cap = 0; c->xent_counter = nullptr;
     c->splitk_ws = nullptr; c->splitk_ws_bytes = 0;

@@ -24,6 +24,13 @@ class Communicator:
         h = C.c_void_p()
         ctx._check(ctx._lib.rst_comm_create(ctx.handle, buf, self.rank, self.world, C.byref(h)))
         self.handle = h
+        # Ranks exchange shares of the global-batch gradient (each divides by B, not B/G) and
+        # the exchange is a plain sum, which NCCL can reduce inside the NVSwitch; the result is
+        # the same average.  RSTORCH_B200_SHARE_GRADIENTS=0 keeps the averaging exchange.
+        import os
+        self.shares = os.environ.get("RSTORCH_B200_SHARE_GRADIENTS", "1") != "0"
+        if self.shares:
+            ctx._check(ctx._lib.rst_comm_share_gradients(h, 1))
 
     @staticmethod
     def new_id() -> bytes:
