@@ -5,6 +5,12 @@ its `B/G` rows; `Linear::backward` divides by the local row count
 (src/module/linear.rs:62-66), so the average over ranks of every dW/db equals
 the full-batch gradient.  The exchange of a layer starts as soon as its
 gradients are queued and overlaps the rest of the backward pass.
+
+A `Communicator` switches its context to exchanging shares: `Linear::backward`
+divides by the global row count `B` instead of `B/G`, and the exchange adds the
+shares up.  The gradients after the exchange are the same averages; between a
+layer's backward and its exchange they hold 1/G of the local-batch gradient.
+A plain sum is what NCCL can reduce inside the NVSwitch.
 """
 from __future__ import annotations
 
